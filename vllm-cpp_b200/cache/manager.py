@@ -41,7 +41,7 @@ class PagedGroup:
     spec: PagedKVSpec
     layers: List[int]                      # cache layer ids, in order
     pool: BlockPool
-    pages: Optional[torch.Tensor] = None   # [len(layers), num_pages, 2, kv_heads, page_size * head_dim]: see csrc/common.cuh (kv_pos)
+    pages: Optional[torch.Tensor] = None   # [len(layers), num_pages, planes, kv_heads, page_size * head_dim]: see csrc/common.cuh (kv_pos)
 
 
 @dataclass
@@ -104,13 +104,13 @@ class CacheManager:
     def bytes_per_page(cache_specs: List[object], page_size: int, dtype: torch.dtype) -> int:
         """Device bytes that one page id costs over all paged cache layers."""
         el = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * s.num_kv_heads * page_size * s.head_dim * el
+        return sum(s.planes * s.num_kv_heads * page_size * s.head_dim * el
                    for s in cache_specs if isinstance(s, PagedKVSpec))
 
     def _allocate_device(self) -> None:
         for g in self.paged:
             s = g.spec
-            g.pages = torch.zeros((len(g.layers), self.num_pages, 2, s.num_kv_heads, self.page_size * s.head_dim),
+            g.pages = torch.zeros((len(g.layers), self.num_pages, s.planes, s.num_kv_heads, self.page_size * s.head_dim),
                                   dtype=self.dtype, device=self.device)
         for g in self.state:
             g.slots = torch.zeros((len(g.layers), self.max_num_seqs) + tuple(g.spec.shape),

@@ -33,13 +33,16 @@ class LayerSpec:
     names to PartSpecs (slots may also be given as keyword arguments); ``names`` maps the same slot
     names to the checkpoint prefixes of the parts' tensors, e.g.
     {"mixer": "model.layers.3.self_attn.", "mixer_norm": "model.layers.3.input_layernorm."}.
+    ``block_params`` are constants of the arrangement itself (a multiplier of its residual branches).
     """
 
     def __init__(self, parts: Optional[Dict[str, PartSpec]] = None, block: str = "prenorm",
-                 names: Optional[Dict[str, str]] = None, **slots: PartSpec):
+                 names: Optional[Dict[str, str]] = None, block_params: Optional[Dict[str, Any]] = None,
+                 **slots: PartSpec):
         self.parts: Dict[str, PartSpec] = dict(parts or {}, **slots)
         self.block = block
         self.names: Dict[str, str] = dict(names or {})
+        self.block_params: Dict[str, Any] = dict(block_params or {})      # the arrangement's own constants
 
     def __getattr__(self, slot):                  # spec.mixer_norm reads spec.parts["mixer_norm"]
         parts = self.__dict__.get("parts", {})
@@ -58,11 +61,14 @@ class LayerCall:
     ``layer`` indexes ``ModelSpec.layers`` (an index may appear twice: the same
     weights run again).  ``cache`` names the cache layer that this call's mixer
     uses; ``writes_cache`` False means the call only reads what an earlier call
-    with the same ``cache`` wrote in this step and in earlier ones.
+    with the same ``cache`` wrote in this step and in earlier ones.  ``state`` (-1: none)
+    names the cache layer that holds per-request state of the call's arrangement (what its
+    ``state_spec`` declares); it belongs to this call alone.
     """
     layer: int
     cache: int
     writes_cache: bool = True
+    state: int = -1
 
 
 @dataclass
@@ -90,9 +96,11 @@ class ModelSpec:
     # embedding -> layers -> final norm -> output product; an architecture that scales its embeddings,
     # caps its logits or adds an output bias registers a subclass that overrides embed() or head().
     model_class: str = "decoder"
+    # Constants of that model class (an embedding scale, the base of its position vector).
+    model_params: Dict[str, Any] = field(default_factory=dict)
 
     def validate(self) -> None:
-        n_cache = 1 + max((c.cache for c in self.run_order), default=-1)
+        n_cache = self.num_cache_layers
         writers = {}
         for i, call in enumerate(self.run_order):
             if not 0 <= call.layer < len(self.layers):
@@ -104,10 +112,18 @@ class ModelSpec:
                 writers[call.cache] = i
             elif call.cache not in writers:
                 raise ValueError(f"run_order[{i}] reads cache {call.cache} before any entry wrote it")
-        missing = [c for c in range(n_cache) if c not in writers]
+        states = {}
+        for i, call in enumerate(self.run_order):
+            if call.state < 0:
+                continue
+            if call.state in writers or call.state in states:
+                raise ValueError(f"run_order[{i}] keeps its state in cache layer {call.state}, which entry "
+                                 f"{writers.get(call.state, states.get(call.state))} already uses")
+            states[call.state] = i
+        missing = [c for c in range(n_cache) if c not in writers and c not in states]
         if missing:
             raise ValueError(f"cache layers {missing} are never written")
 
     @property
     def num_cache_layers(self) -> int:
-        return 1 + max((c.cache for c in self.run_order), default=-1)
+        return 1 + max((max(c.cache, c.state) for c in self.run_order), default=-1)

@@ -51,11 +51,14 @@ def resolve_architecture(config: dict, model_arch: str = "") -> Tuple[object, Mo
     name = model_arch
     if not name:
         archs = config.get("architectures")
-        if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
+        if isinstance(archs, list) and archs and isinstance(archs[0], str):
+            name = archs[0]
+        elif isinstance(config.get("architecture"), str):       # some designs name themselves in one string
+            name = config["architecture"]
+        else:
             raise ConfigError(
-                "config.json has no 'architectures' list and no model_arch was given; "
+                "config.json has no 'architectures' list (nor an 'architecture' name) and no model_arch was given; "
                 f"known architectures: {known_architectures()}")
-        name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"Unknown model architecture: {name!r}; known: {known_architectures()}")
     typed, spec = _ARCHITECTURES[name](config)

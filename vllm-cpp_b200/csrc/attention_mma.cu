@@ -52,6 +52,8 @@ struct MmaAttnArgs {
     float scale;
     int num_pages;                 // pages of the cache: a table entry outside [0, num_pages) is read as page 0
                                    // and VCB_STATUS_BAD_PAGE goes to the status word
+    int planes;                    // 2: a page holds keys, then values; 1: one plane of rows that are key and value
+                                   // at once (attention over cached latent rows, queries already in their space)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -315,8 +317,8 @@ attention_decode_kernel(MmaAttnArgs a) {
             PageWindow pw;
             const PageDiv pd(a.page);
             pw.init(bt, pd.div(my0 * BN), hi, a.page, lane, a.num_pages);
-            const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
-                         v_off = (size_t)a.nkv * a.page * D;
+            const size_t page_stride = (size_t)a.planes * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
+                         v_off = (size_t)(a.planes - 1) * a.nkv * a.page * D;
             for (int tile = my0; tile < my1; ++tile, ++it) {
                 const int st = it % STAGES;
                 if (!waited && (tile + 1) * BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's row
@@ -691,8 +693,8 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         PageWindow pw;
         const PageDiv pd(a.page);
         pw.init(bt, pd.div(tile0 * TKT), hi, a.page, lane, a.num_pages);
-        const size_t page_stride = (size_t)2 * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
-                     v_off = (size_t)a.nkv * a.page * D;
+        const size_t page_stride = (size_t)a.planes * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
+                     v_off = (size_t)(a.planes - 1) * a.nkv * a.page * D;
         // a tile's addresses are worked out before its stage is waited for
         TilePiece pc = tile_piece<D, TKT>(tile0 * TKT, lo, hi, pw, a.cache, head_base, page_stride, pd, lane);
         if (warp == 0) {
@@ -950,38 +952,60 @@ static int check_common(int nh, int nkv, int d, int page, int window, int num_pa
 // Scratch for the split-KV merge (nsplit > 1): part_o needs n_list*nh*nsplit*d floats, part_ml
 // n_list*nh*nsplit*2 floats, counters n_list*nkv ints that are zero when the kernel starts (it
 // leaves them zero).
+VCB_EXPORT int vcb_attention_decode_mma_planes(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* req_list, int n_list, int nsplit, float* part_o,
+                                               float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
+                                               int d, int page, int window, float scale, int num_pages, int* status,
+                                               int planes, void* stream) {
+    if (n_list <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window, num_pages);
+    if (c) return c;
+    if (planes != 1 && planes != 2) return VCB_ERR_BAD_ARG;
+    if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
+                  page, window, scale, num_pages, planes};
+    cudaStream_t s = (cudaStream_t)stream;
+    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+}
+
 VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* req_list, int n_list, int nsplit, float* part_o,
                                         float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
                                         int d, int page, int window, float scale, int num_pages, int* status,
                                         void* stream) {
-    if (n_list <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window, num_pages);
-    if (c) return c;
-    if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
-    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
-                  page, window, scale, num_pages};
-    cudaStream_t s = (cudaStream_t)stream;
-    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+    return vcb_attention_decode_mma_planes(q, cache, out, q_start, ctx_lens, block_table, bt_stride, req_list, n_list, nsplit,
+                                           part_o, part_ml, counters, split_tiles, nh, nkv, d, page, window, scale,
+                                           num_pages, status, 2, stream);
 }
 
 // Prompt portions (and, in mixed batches, single tokens) on tcgen05 tensor cores: head sizes 64 and 128,
 // pages of a multiple of 8 tokens; tiles (tile_req, tile_row0) of 128 packed rows, row = token * G + head
 // in group.
+VCB_EXPORT int vcb_attention_prefill_tc_planes(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* tile_req, const int* tile_row0, int n_tiles, int nh,
+                                               int nkv, int d, int page, int window, float scale, int num_pages,
+                                               int* status, int planes, void* stream) {
+    if (n_tiles <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window, num_pages);
+    if (c) return c;
+    if (planes != 1 && planes != 2) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
+                  window, scale, num_pages, planes};
+    return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
+}
+
 VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* tile_req, const int* tile_row0, int n_tiles, int nh,
                                         int nkv, int d, int page, int window, float scale, int num_pages,
                                         int* status, void* stream) {
-    if (n_tiles <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window, num_pages);
-    if (c) return c;
-    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale, num_pages};
-    return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
+    return vcb_attention_prefill_tc_planes(q, cache, out, q_start, ctx_lens, block_table, bt_stride, tile_req, tile_row0,
+                                           n_tiles, nh, nkv, d, page, window, scale, num_pages, status, 2, stream);
 }
 
 // ------------------------------------------------ no-allocation entry point
@@ -1060,7 +1084,7 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
     }
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, req_list, nullptr, nsplit > 1 ? part_o : nullptr, part_ml, nsplit > 1 ? counters : nullptr,
-                  status, nullptr, bt_stride, nh, nkv, page, window, scale, num_pages};
+                  status, nullptr, bt_stride, nh, nkv, page, window, scale, num_pages, 2};
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
 

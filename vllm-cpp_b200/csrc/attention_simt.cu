@@ -1,4 +1,4 @@
-// Paged attention over the cache, plain SIMT form, for any head size up to 256
+// Paged attention over the cache, plain SIMT form, for any head size up to 512
 // and both storage types.  It is the 32-bit path's attention and the reference
 // that the tensor-core kernels are compared with.
 //
@@ -15,12 +15,13 @@
 // not kept: a row always has at least its own key.
 #include "common.cuh"
 
-#define ATT_MAX_D 256
+#define ATT_MAX_D 512
 #define ATT_WARPS 4
 
 struct AttnArgs {
     const void* q;              // [n_tokens, nh * d]
-    const void* cache;          // [pages][2][nkv][page][d]
+    const void* cache;          // [pages][planes][nkv][page][d]; planes 2: keys, then values; planes 1: a row is
+                                // key and value at once (attention over cached latent rows)
     void* out;                  // [n_tokens, nh * d]
     const int* positions;
     const int* req_of_token;
@@ -29,9 +30,10 @@ struct AttnArgs {
     float scale;
     int num_pages;              // a table entry outside [0, num_pages) is not read through: the key is left
     int* status;                // out and VCB_STATUS_BAD_PAGE is recorded here (may be null)
+    int planes;
 };
 
-template <typename T>
+template <typename T, int MAXD>
 __global__ void attention_simt_kernel(AttnArgs a) {
     extern __shared__ float qs_all[];
     pdl_start();
@@ -47,13 +49,13 @@ __global__ void attention_simt_kernel(AttnArgs a) {
     for (int i = lane; i < a.d; i += 32) qs[i] = to_f32<T>(qrow[i]) * a.scale;
     __syncwarp();
 
-    const size_t page_elems = (size_t)2 * a.nkv * a.page * a.d;
-    const size_t v_off = (size_t)a.nkv * a.page * a.d;
+    const size_t page_elems = (size_t)a.planes * a.nkv * a.page * a.d;
+    const size_t v_off = (size_t)(a.planes - 1) * a.nkv * a.page * a.d;
     const T* cache = (const T*)a.cache;
 
-    float o[ATT_MAX_D / 32];
+    float o[MAXD / 32];
 #pragma unroll
-    for (int k = 0; k < ATT_MAX_D / 32; ++k) o[k] = 0.0f;
+    for (int k = 0; k < MAXD / 32; ++k) o[k] = 0.0f;
     float m = -INFINITY, l = 0.0f;
     const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
 
@@ -84,7 +86,7 @@ __global__ void attention_simt_kernel(AttnArgs a) {
         const float p = valid ? expf(s - m_new) : 0.0f;
         l = l * corr + warp_sum(p);
 #pragma unroll
-        for (int k = 0; k < ATT_MAX_D / 32; ++k) o[k] *= corr;
+        for (int k = 0; k < MAXD / 32; ++k) o[k] *= corr;
         const int nvalid = min(32, pos - kb + 1);
         for (int jj = 0; jj < nvalid; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
@@ -92,7 +94,7 @@ __global__ void attention_simt_kernel(AttnArgs a) {
             const T* vr = cache + off + v_off;
             const int slot = (kb + jj) % a.page;
 #pragma unroll
-            for (int k = 0; k < ATT_MAX_D / 32; ++k) {
+            for (int k = 0; k < MAXD / 32; ++k) {
                 const int dim = lane + 32 * k;
                 if (dim < a.d) o[k] += pj * to_f32<T>(vr[kv_pos(dim, slot, a.d, a.page, (int)sizeof(T))]);
             }
@@ -102,27 +104,42 @@ __global__ void attention_simt_kernel(AttnArgs a) {
     T* orow = (T*)a.out + ((size_t)t * a.nh + h) * a.d;
     const float inv = 1.0f / l;
 #pragma unroll
-    for (int k = 0; k < ATT_MAX_D / 32; ++k) {
+    for (int k = 0; k < MAXD / 32; ++k) {
         const int dim = lane + 32 * k;
         if (dim < a.d) orow[dim] = from_f32<T>(o[k] * inv);
     }
 }
 
-VCB_EXPORT int vcb_attention_simt(const void* q, const void* cache, void* out, const int* positions,
+VCB_EXPORT int vcb_attention_simt_planes(const void* q, const void* cache, void* out, const int* positions,
                                   const int* req_of_token, const int* block_table, int bt_stride,
                                   int n_tokens, int nh, int nkv, int d, int page, int window,
-                                  float scale, int num_pages, int* status, int dtype, void* stream) {
+                                  float scale, int num_pages, int* status, int planes, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || d > ATT_MAX_D || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0 || num_pages < 0)
+    if (d <= 0 || d > ATT_MAX_D || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || window < 0 || num_pages < 0 ||
+        (planes != 1 && planes != 2))
         return VCB_ERR_BAD_ARG;
     AttnArgs a{q, cache, out, positions, req_of_token, block_table, bt_stride, n_tokens, nh, nkv, d,
-               page, window, scale, num_pages, status};
+               page, window, scale, num_pages, status, planes};
     const long long items = (long long)n_tokens * nh;
     const int blocks = (int)((items + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32) vcb_launch(attention_simt_kernel<float>, blocks, ATT_WARPS * 32, smem, s, a);
-    else if (dtype == VCB_BF16) vcb_launch(attention_simt_kernel<__nv_bfloat16>, blocks, ATT_WARPS * 32, smem, s, a);
-    else return VCB_ERR_BAD_ARG;
+    const bool wide = d > 256;          // the output row in registers: 8 floats a lane up to 256, 16 beyond
+    if (dtype == VCB_F32) {
+        if (wide) vcb_launch(attention_simt_kernel<float, 512>, blocks, ATT_WARPS * 32, smem, s, a);
+        else vcb_launch(attention_simt_kernel<float, 256>, blocks, ATT_WARPS * 32, smem, s, a);
+    } else if (dtype == VCB_BF16) {
+        if (wide) vcb_launch(attention_simt_kernel<__nv_bfloat16, 512>, blocks, ATT_WARPS * 32, smem, s, a);
+        else vcb_launch(attention_simt_kernel<__nv_bfloat16, 256>, blocks, ATT_WARPS * 32, smem, s, a);
+    } else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
+}
+
+// Keys and values in planes of their own (planes = 2), the form every cache with separate keys and values has.
+VCB_EXPORT int vcb_attention_simt(const void* q, const void* cache, void* out, const int* positions,
+                                  const int* req_of_token, const int* block_table, int bt_stride,
+                                  int n_tokens, int nh, int nkv, int d, int page, int window,
+                                  float scale, int num_pages, int* status, int dtype, void* stream) {
+    return vcb_attention_simt_planes(q, cache, out, positions, req_of_token, block_table, bt_stride, n_tokens, nh, nkv, d,
+                                     page, window, scale, num_pages, status, 2, dtype, stream);
 }

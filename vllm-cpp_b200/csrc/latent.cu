@@ -1,0 +1,180 @@
+// Kernels of latent attention: keys and values of all heads are projections of one low-rank row per
+// token (the latent), and only that row is cached.
+//
+//   latent_cache_write_kernel   c = raw / sqrt(mean(raw^2) + eps) * gain  ->  the token's slot of a cache
+//                               whose pages hold one plane of rows (kv_pos layout, common.cuh)
+//   headwise_linear_kernel      out[t, h, :] = x[t, h, :] W_h^T for every head h (a block-diagonal product):
+//                               queries into the latent space (W_h = Wuk_h^T) so that scores are taken against
+//                               the cached rows directly, and attention's result back out of it (W_h = Wuv_h),
+//                               there with an optional sigmoid gate on the result
+//
+// With the queries absorbed, attention over the latent rows is multi-query attention with one shared
+// key/value row of `rank` elements per token, and runs on the engine's attention kernels with the value
+// plane of a page being its key plane.  The reference has no such layer.
+#include "common.cuh"
+
+// ------------------------------------------------------ norm of the latent + cache write
+// One warp per token.  raw: [n, ld] rows of the product that made it (the latent's columns start at raw).
+template <typename T>
+__global__ void latent_cache_write_kernel(const T* __restrict__ raw, int ld, const float* __restrict__ gain,
+                                          const int* __restrict__ positions, const int* __restrict__ req_of_token,
+                                          const int* __restrict__ block_table, int bt_stride, T* __restrict__ cache,
+                                          size_t page_stride, int n_tokens, int rank, int page, float eps,
+                                          int num_pages, int* status) {
+    pdl_start();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    const T* row = raw + (size_t)t * ld;
+    float ss = 0.0f;
+    for (int i = lane; i < rank; i += 32) {
+        const float v = to_f32<T>(row[i]);
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)rank + eps);
+    const int pos = positions[t];
+    const int lp = pos / page, slot = pos - lp * page;
+    const int pg = lp < bt_stride ? block_table[(size_t)req_of_token[t] * bt_stride + lp] : -1;
+    if ((unsigned)pg >= (unsigned)num_pages) {
+        if (status && lane == 0) atomicCAS(status, 0, VCB_STATUS_BAD_PAGE);
+        return;
+    }
+    T* dst = cache + (size_t)pg * page_stride;
+    for (int i = lane; i < rank; i += 32)
+        dst[kv_pos(i, slot, rank, page, (int)sizeof(T))] = from_f32<T>((to_f32<T>(row[i]) * r) * gain[i]);
+}
+
+VCB_EXPORT int vcb_latent_cache_write(const void* raw, int ld, const float* gain, const int* positions,
+                                      const int* req_of_token, const int* block_table, int bt_stride, void* cache,
+                                      long long page_stride, int n_tokens, int rank, int page, float eps, int num_pages,
+                                      int* status, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (rank <= 0 || page <= 0 || ld < rank || page_stride < (long long)page * rank || num_pages <= 0) return VCB_ERR_BAD_ARG;
+    const int warps = 4, blocks = (n_tokens + warps - 1) / warps;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        vcb_launch(latent_cache_write_kernel<float>, blocks, warps * 32, 0, s, (const float*)raw, ld, gain, positions,
+                   req_of_token, block_table, bt_stride, (float*)cache, (size_t)page_stride, n_tokens, rank, page, eps,
+                   num_pages, status);
+    else if (dtype == VCB_BF16)
+        vcb_launch(latent_cache_write_kernel<__nv_bfloat16>, blocks, warps * 32, 0, s, (const __nv_bfloat16*)raw, ld, gain,
+                   positions, req_of_token, block_table, bt_stride, (__nv_bfloat16*)cache, (size_t)page_stride, n_tokens,
+                   rank, page, eps, num_pages, status);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------ per-head products
+// out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]   (w: [heads, N, K] contiguous; x rows ldx apart with head h
+// at column h * K + x0; out rows ldo apart with head h at column h * N), float accumulation.
+// gate (may be null; rows ldg apart, head h at column h * N): out *= sigmoid(gate).
+// 64 x 64 output tile per CTA and head, 16-deep k slices in shared memory, a 4 x 4 register tile per thread,
+// every edge guarded.  With few tokens the weights are read once and the kernel runs at the rate they
+// stream at; long portions in bfloat16 go to the library's batched product instead (ops.headwise_linear).
+#define HT 64
+#define HK 16
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+headwise_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, const T* __restrict__ gate,
+                       int M, int N, int K, int ldx, int ldo, int ldg) {
+    __shared__ float As[HK][HT + 1];
+    __shared__ float Ws[HK][HT + 1];
+    pdl_start();
+    const int h = blockIdx.z;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int m0 = blockIdx.y * HT, n0 = blockIdx.x * HT;
+    const T* xh = x + (size_t)h * K;
+    const T* wh = w + (size_t)h * N * K;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += HK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = threadIdx.x + e * 256;
+            const int r = idx / HK, kk = idx % HK;
+            const int k = k0 + kk;
+            As[kk][r] = (m0 + r < M && k < K) ? to_f32<T>(xh[(size_t)(m0 + r) * ldx + k]) : 0.0f;
+            Ws[kk][r] = (n0 + r < N && k < K) ? to_f32<T>(wh[(size_t)(n0 + r) * K + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HK; ++kk) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (gate) v *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)m * ldg + (size_t)h * N + n])));
+            out[(size_t)m * ldo + (size_t)h * N + n] = from_f32<T>(v);
+        }
+    }
+}
+
+VCB_EXPORT int vcb_headwise_linear(const void* x, const void* w, void* out, const void* gate, int M, int heads, int N,
+                                   int K, int ldx, int ldo, int ldg, int dtype, void* stream) {
+    if (M <= 0 || heads <= 0 || N <= 0) return 0;
+    if (K <= 0 || ldx < heads * K || ldo < heads * N || (gate && ldg < heads * N) || heads > 65535) return VCB_ERR_BAD_ARG;
+    dim3 grid((N + HT - 1) / HT, (M + HT - 1) / HT, heads);
+    if (grid.y > 65535) return VCB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        vcb_launch(headwise_linear_kernel<float>, grid, 256, 0, s, (const float*)x, (const float*)w, (float*)out,
+                   (const float*)gate, M, N, K, ldx, ldo, ldg);
+    else if (dtype == VCB_BF16)
+        vcb_launch(headwise_linear_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                   (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, M, N, K, ldx, ldo, ldg);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// out[t, i] *= sigmoid(gate[t, i]) in place (rows ldo and ldg apart): the gate where the product before it
+// was the library's.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ gate, int n, int cols, int ldo, int ldg) {
+    pdl_start();
+    const size_t total = (size_t)n * cols;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / cols, i = idx - t * cols;
+        const float v = to_f32<T>(out[t * ldo + i]);
+        out[t * ldo + i] = from_f32<T>(v * (1.0f / (1.0f + expf(-to_f32<T>(gate[t * ldg + i])))));
+    }
+}
+
+VCB_EXPORT int vcb_sigmoid_gate(void* out, const void* gate, int n, int cols, int ldo, int ldg, int dtype, void* stream) {
+    if (n <= 0 || cols <= 0) return 0;
+    if (ldo < cols || ldg < cols) return VCB_ERR_BAD_ARG;
+    const size_t total = (size_t)n * cols;
+    const int blocks = (int)((total + 255) / 256 < (size_t)vcb_sm_count() * 8 ? (total + 255) / 256 : (size_t)vcb_sm_count() * 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        vcb_launch(sigmoid_gate_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate, n, cols, ldo, ldg);
+    else if (dtype == VCB_BF16)
+        vcb_launch(sigmoid_gate_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, n,
+                   cols, ldo, ldg);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}

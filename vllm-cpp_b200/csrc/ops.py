@@ -44,6 +44,15 @@ _SIGNATURES = {
     "vcb_sample": [_P, _I, _I, _P, _P, _P, _I, _P],
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "vcb_random_normal": [_P, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, _F, _F, _I, _P],
+    "vcb_attention_simt_planes": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _P],
+    "vcb_attention_decode_mma_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
+    "vcb_attention_prefill_tc_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
+    "vcb_embedding_sinusoid": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P, _I, _P],
+    "vcb_token_shift": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "vcb_gated_norm_residual": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _F, _I, _P],
+    "vcb_latent_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, ctypes.c_longlong, _I, _I, _I, _F, _I, _P, _I, _P],
+    "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _P],
 }
 
 
@@ -212,18 +221,24 @@ def rope_cache_write(qkv, bias, positions, req_of_token, block_table, denom, q_o
         "rope_cache_write")
 
 
+SIMT_MAX_HEAD_DIM = 512
+
+
 def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_heads: int,
-                   num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> None:
+                   num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, planes: int = 2) -> None:
+    """Plain paged attention.  ``planes`` 2: a page holds keys, then values; 1: one plane of rows that serve
+    as key and as value (cached latent rows)."""
     n = q.shape[0]
-    _need(head_dim <= 256, f"head_dim {head_dim} exceeds 256, the largest this attention kernel takes")
+    _need(head_dim <= SIMT_MAX_HEAD_DIM, f"head_dim {head_dim} exceeds {SIMT_MAX_HEAD_DIM}, the largest this attention kernel takes")
+    _need(planes in (1, 2), "planes must be 1 or 2")
     _need(q.shape == (n, num_heads * head_dim) and out.shape == q.shape and out.dtype == q.dtype, "q/out shape")
     _need(num_heads % num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads")
     _need(cache.dtype == q.dtype, "cache and q must share a storage type")
-    _check(lib().vcb_attention_simt(
+    _check(lib().vcb_attention_simt_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(positions, "positions", torch.int32),
         _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], n, num_heads, num_kv_heads, head_dim, page_size, window, float(scale),
-        cache.shape[0], status_tensor(q.device).data_ptr(), dtype_code(q.dtype), _stream()), "attention_simt")
+        cache.shape[0], status_tensor(q.device).data_ptr(), planes, dtype_code(q.dtype), _stream()), "attention_simt")
 
 
 MMA_HEAD_DIMS = (64, 128)
@@ -233,7 +248,7 @@ DECODE_MAX_SPLITS = 32
 
 def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
                          part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                         window: int, scale: float, split_tiles=None) -> None:
+                         window: int, scale: float, split_tiles=None, planes: int = 2) -> None:
     """Split-KV tensor-core attention for requests that bring one token each (bfloat16).  The grid has
     ``nsplit`` columns; without ``split_tiles`` every request's keys are cut into that many equal parts,
     with it (int32 [1] on the device: tiles of DECODE_KEY_TILE keys per split) a request takes as many
@@ -247,7 +262,8 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         _need(part_o is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2
               and counters is not None and counters.numel() >= n_list * num_kv_heads,
               "attention_decode_mma: scratch for the split merge is too small")
-    _check(lib().vcb_attention_decode_mma(
+    _need(planes in (1, 2), "planes must be 1 or 2")
+    _check(lib().vcb_attention_decode_mma_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], None if req_list is None else _dev(req_list, "req_list", torch.int32),
@@ -256,7 +272,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         None if counters is None else _dev(counters, "counters", torch.int32),
         None if split_tiles is None else _dev(split_tiles, "split_tiles", torch.int32),
         num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
-        status_tensor(q.device).data_ptr(), _stream()), "attention_decode_mma")
+        status_tensor(q.device).data_ptr(), planes, _stream()), "attention_decode_mma")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)      # head sizes of the tcgen05 prefill attention kernel
@@ -265,7 +281,7 @@ TC_ATTENTION_TILE_ROWS = 128     # packed rows per tile of its work list
 
 def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                         scale: float) -> None:
+                         scale: float, planes: int = 2) -> None:
     """Attention for portions of any length on tcgen05 tensor cores (scores and output tiles in tensor
     memory); head sizes 64 and 128, bfloat16, pages of a multiple of 8 slots, tiles of 128 packed rows."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -274,12 +290,13 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
           f"attention_prefill_tc takes head sizes {TC_ATTENTION_HEAD_DIMS} and pages of a multiple of 8 slots")
     n_tiles = tile_req.numel()
     _need(tile_row0.numel() == n_tiles, "one first row per tile")
-    _check(lib().vcb_attention_prefill_tc(
+    _need(planes in (1, 2), "planes must be 1 or 2")
+    _check(lib().vcb_attention_prefill_tc_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
         n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
-        status_tensor(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+        status_tensor(q.device).data_ptr(), planes, _stream()), "attention_prefill_tc")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -728,6 +745,101 @@ def linear_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_scale: O
     only where ``linear_gated_fuses`` said yes."""
     _need(linear_gated_fuses(x.shape[0], w), "linear_gated: ask linear_gated_fuses first")
     gemm_bf16_tcgen05(x, w, out, x_scale=x_scale, gated=True)
+
+
+# ------------------------------------------------- residual stream: shift, gates, norms on results
+def embedding_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                       residual: torch.Tensor, scale: float) -> None:
+    """residual[t, i] = float(table[ids[t], i]) * scale + (sin if i even else cos)(positions[t] * inv_freq[i // 2])."""
+    n, hidden = residual.shape
+    _need(table.dim() == 2 and table.shape[1] == hidden, "embedding table width differs from the residual's")
+    _need(ids.numel() == n and positions.numel() == n, "one id and one position per residual row")
+    _need(inv_freq.numel() >= (hidden + 1) // 2, "one frequency per pair of coordinates")
+    _check(lib().vcb_embedding_sinusoid(_dev(table, "table"), _dev(ids, "ids", torch.int32),
+                                        _dev(positions, "positions", torch.int32), _dev(inv_freq, "inv_freq", torch.float32),
+                                        _dev(residual, "residual", torch.float32), n, hidden, table.shape[0], float(scale),
+                                        status_tensor(table.device).data_ptr(), dtype_code(table.dtype), _stream()),
+           "embedding_sinusoid")
+
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, shifted: torch.Tensor,
+                plain: Optional[torch.Tensor], q_start, req_of_token, positions, state_slots) -> None:
+    """shifted[t] = x[t] + (x[t-1] - x[t]) * mu in the activations' type; x float32 [n, hidden].  The row before
+    a request's first row of the step is zero at position 0, else the request's slot of ``state`` (float32
+    [slots, hidden]), which then receives the request's last row of this step.  ``plain`` (optional): x in the
+    activations' type."""
+    n, hidden = x.shape
+    _need(shifted.shape == x.shape and (plain is None or (plain.shape == x.shape and plain.dtype == shifted.dtype)),
+          "token_shift: outputs must have the input's shape")
+    _need(mu.numel() == hidden and state.dim() == 2 and state.shape[1] == hidden, "token_shift: widths differ")
+    _check(lib().vcb_token_shift(_dev(x, "x", torch.float32), _dev(mu, "mu", torch.float32), _dev(state, "state", torch.float32),
+                                 _dev(shifted, "shifted"), None if plain is None else _dev(plain, "plain"),
+                                 _dev(q_start, "q_start", torch.int32), _dev(req_of_token, "req_of_token", torch.int32),
+                                 _dev(positions, "positions", torch.int32), _dev(state_slots, "state_slots", torch.int32),
+                                 n, hidden, dtype_code(shifted.dtype), _stream()), "token_shift")
+
+
+def gated_norm_residual(y: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
+                        gain: torch.Tensor, x: torch.Tensor, plain: Optional[torch.Tensor], mult: float, eps: float) -> None:
+    """z = y * sigmoid(gate + gate_bias) (no gate: z = y);  x += mult * z / sqrt(mean(z^2) + eps) * gain, in float32
+    in place; ``gain``: one number or a vector.  ``plain`` (optional): the new x in the activations' type."""
+    n, hidden = x.shape
+    _need(y.shape == x.shape and (gate is None or (gate.shape == x.shape and gate.dtype == y.dtype)), "gated_norm_residual: shapes")
+    _need(gate_bias is None or gate_bias.numel() == hidden, "gated_norm_residual: one bias value per column")
+    _need(gain.numel() in (1, hidden), "gated_norm_residual: gain is one number or one per column")
+    _need(plain is None or (plain.shape == x.shape and plain.dtype == y.dtype), "gated_norm_residual: plain output")
+    _check(lib().vcb_gated_norm_residual(_dev(y, "y"), None if gate is None else _dev(gate, "gate"),
+                                         None if gate_bias is None else _dev(gate_bias, "gate_bias", torch.float32),
+                                         _dev(gain, "gain", torch.float32), 0 if gain.numel() == 1 else 1,
+                                         _dev(x, "x", torch.float32), None if plain is None else _dev(plain, "plain"),
+                                         n, hidden, float(mult), float(eps), dtype_code(y.dtype), _stream()),
+           "gated_norm_residual")
+
+
+# ------------------------------------------------------------------ latent attention
+def latent_cache_write(raw: torch.Tensor, gain: torch.Tensor, positions, req_of_token, block_table, cache: torch.Tensor,
+                       *, page_size: int, eps: float) -> None:
+    """RMS norm (gain vector, float statistics) of the rows of ``raw`` ([n, rank], rows may be strided) and their
+    write into the tokens' slots of a one-plane cache [pages, page_size * rank] (kv_pos layout)."""
+    n, rank = raw.shape
+    _need(raw.stride(1) == 1 and raw.is_cuda, "latent_cache_write: rows with unit inner stride on the GPU")
+    _need(cache.dtype == raw.dtype and cache.is_contiguous() and cache.numel() == cache.shape[0] * page_size * rank,
+          "latent_cache_write: a one-plane cache of the activations' type")
+    _need(gain.numel() == rank, "latent_cache_write: one gain per latent coordinate")
+    _check(lib().vcb_latent_cache_write(raw.data_ptr(), raw.stride(0), _dev(gain, "gain", torch.float32),
+                                        _dev(positions, "positions", torch.int32), _dev(req_of_token, "req_of_token", torch.int32),
+                                        _dev(block_table, "block_table", torch.int32), block_table.shape[1], cache.data_ptr(),
+                                        page_size * rank, n, rank, page_size, float(eps), cache.shape[0],
+                                        status_tensor(raw.device).data_ptr(), dtype_code(raw.dtype), _stream()),
+           "latent_cache_write")
+
+
+HEADWISE_LIBRARY_TOKENS = 128      # bfloat16 portions longer than this run the library's batched product
+
+
+def headwise_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, :] = x[t, h, :] @ w[h]^T for every head: x [n, heads * K] (rows may be strided), w [heads, N, K],
+    out [n, heads * N]; with ``gate`` ([n, heads * N], rows may be strided) out *= sigmoid(gate).  float32 and
+    short bfloat16 steps: this library's kernel; long bfloat16 portions: the library's batched product, then
+    the gate as a kernel."""
+    heads, N, K = w.shape
+    n = x.shape[0]
+    _need(x.shape == (n, heads * K) and out.shape == (n, heads * N) and x.stride(1) == 1 and out.stride(1) == 1,
+          "headwise_linear: x [n, heads * K], out [n, heads * N]")
+    _need(w.is_contiguous() and x.dtype == w.dtype == out.dtype, "headwise_linear: one type, contiguous weights")
+    if gate is not None:
+        _need(gate.shape == out.shape and gate.stride(1) == 1 and gate.dtype == out.dtype, "headwise_linear: gate like out")
+    if x.dtype == torch.bfloat16 and n > HEADWISE_LIBRARY_TOKENS:
+        xh = x.unflatten(1, (heads, K)).transpose(0, 1)             # [heads, n, K]
+        oh = out.unflatten(1, (heads, N)).transpose(0, 1)           # [heads, n, N]
+        oh.copy_(torch.bmm(xh, w.transpose(1, 2)))
+        if gate is not None:
+            _check(lib().vcb_sigmoid_gate(out.data_ptr(), gate.data_ptr(), n, heads * N, out.stride(0), gate.stride(0),
+                                          dtype_code(out.dtype), _stream()), "sigmoid_gate")
+        return
+    _check(lib().vcb_headwise_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), None if gate is None else gate.data_ptr(),
+                                     n, heads, N, K, x.stride(0), out.stride(0), 0 if gate is None else gate.stride(0),
+                                     dtype_code(x.dtype), _stream()), "headwise_linear")
 
 
 def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:

@@ -28,105 +28,23 @@ MAX_HEAD_DIM = 256
 _warned_head_dims = set()
 
 
-@register_mixer("attention")
-class PagedAttention(Mixer):
-    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 qkv_bias: bool, out_bias: bool, window: int, position: PartSpec, dtype, device):
-        if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
-            raise ValueError(f"attention: {num_heads} heads cannot share {num_kv_heads} kv heads")
-        if head_dim <= 0 or head_dim % 2:
-            raise ValueError(f"attention: head_dim {head_dim} must be positive and even")
-        if head_dim > MAX_HEAD_DIM:
-            raise ValueError(f"attention: head_dim {head_dim} exceeds {MAX_HEAD_DIM}, the largest the kernels take")
-        if out_bias:
-            raise ValueError("attention: a bias on the output projection is not built")
-        if window < 0:
-            raise ValueError("attention: window must be 0 (all keys) or positive")
-        self.hidden, self.nh, self.nkv, self.d = hidden_size, num_heads, num_kv_heads, head_dim
-        self.qkv_bias, self.window = bool(qkv_bias), int(window)
-        self.dtype, self.device = dtype, device
-        self.position = build_part(POSITION_ENCODINGS, "position encoding", position, dtype=dtype, device=device)
-        # 1/sqrtf(d) in float, as src/layers/attention.cpp:126 computes it
-        self.scale = float(np.float32(1.0) / np.sqrt(np.float32(head_dim)))
-        self.w_qkv = None
-        self.b_qkv = None
-        self.w_o = None
-
-    # -- tensors
-    def param_specs(self) -> Dict[str, ParamSpec]:
-        q, kv = self.nh * self.d, self.nkv * self.d
-        specs = {"q_proj.weight": ParamSpec((q, self.hidden)),
-                 "k_proj.weight": ParamSpec((kv, self.hidden)),
-                 "v_proj.weight": ParamSpec((kv, self.hidden)),
-                 "o_proj.weight": ParamSpec((self.hidden, q))}
-        if self.qkv_bias:
-            specs.update({"q_proj.bias": ParamSpec((q,), "bias"),
-                          "k_proj.bias": ParamSpec((kv,), "bias"),
-                          "v_proj.bias": ParamSpec((kv,), "bias")})
-        for name, s in self.position.param_specs().items():
-            specs["position." + name] = s
-        return specs
-
-    def load_params(self, tensors):
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
-                                tensors["v_proj.weight"]], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
-        if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
-                                    tensors["v_proj.bias"]], dim=0).contiguous()
-        self.position.load_params({k[len("position."):]: v for k, v in tensors.items()
-                                   if k.startswith("position.")})
-
-        if self.dtype == torch.bfloat16 and self.d not in ops.MMA_HEAD_DIMS and self.d not in _warned_head_dims:
-            _warned_head_dims.add(self.d)
-            print(f"[vllm_cpp_b200] warning: head size {self.d} has no tensor-core attention kernel "
-                  f"(those take {ops.MMA_HEAD_DIMS}); bfloat16 attention runs the plain kernel, one warp per "
-                  "token and head, many times slower", file=sys.stderr, flush=True)
-
-    # -- cache
-    def cache_spec(self):
-        return PagedKVSpec(self.nkv, self.d, self.window)
-
-    def workspace_bytes(self, n_tokens, n_reqs):
-        q = self.nh * self.d
-        return workspace_piece((n_tokens, q + 2 * self.nkv * self.d), self.dtype) + 2 * workspace_piece((n_tokens, q), self.dtype)
-
-    # -- run
-    def fuses_norm(self, n_tokens):
-        return ops.linear_fuses_norm(n_tokens, self.w_qkv) and ops.linear_fuses_norm(n_tokens, self.w_o)
-
-    def forward(self, x, out, step, cache, writes_cache, ws, x_scale=None, fuse=None):
-        n = x.shape[0]
-        mark = ws.mark()
-        qkv = ws.take((n, (self.nh + 2 * self.nkv) * self.d), self.dtype)
-        ops.linear(x, self.w_qkv, qkv, x_scale=x_scale)
-        q = ws.take((n, self.nh * self.d), self.dtype)
-        block_table = step.block_tables[cache.group]
-        fused = self.position.fused()
-        bias = self.b_qkv
-        if fused is None:
-            # An encoding the fused kernel does not know: bias first, then the
-            # encoding's own code on q and k, then the plain copy into the cache.
-            if bias is not None:
-                ops.add_bias(qkv, bias)
-                bias = None
-            q3 = qkv[:, : self.nh * self.d].unflatten(1, (self.nh, self.d))
-            k3 = qkv[:, self.nh * self.d: (self.nh + self.nkv) * self.d].unflatten(1, (self.nkv, self.d))
-            self.position.apply(q3, k3, step.positions)
-            fused = {"rotary_dim": 0, "pairing": 0, "denom": None}
-        ops.rope_cache_write(qkv, bias, step.positions, step.req_of_token, block_table, fused["denom"], q,
-                             cache.pages, num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
-                             rotary_dim=fused["rotary_dim"], pairing=fused["pairing"],
-                             page_size=cache.page_size, write_kv=writes_cache)
-        attn = ws.take((n, self.nh * self.d), self.dtype)
-        self.attend(q, attn, step, cache, block_table)
-        ops.linear(attn, self.w_o, out, fuse=fuse)
-        ws.release(mark)
+class PagedAttentionKernels(Mixer):
+    """What a mixer needs to run the engine's paged attention kernels on queries it has made: the per-step
+    work lists, the kernels' scratch and the choice of kernel.  A subclass sets ``nh`` (query heads),
+    ``nkv`` (heads of the cache), ``d`` (width of a cached row), ``window``, ``scale``, ``dtype`` and
+    ``planes`` (PagedKVSpec.planes: 2 for keys and values, 1 for rows that are both)."""
+    planes = 2
 
     # -- work lists and kernel choice
     def _tensor_core_path(self) -> bool:
         return self.dtype == torch.bfloat16 and self.d in ops.MMA_HEAD_DIMS
 
+    def warn_if_plain(self) -> None:
+        if self.dtype == torch.bfloat16 and self.d not in ops.MMA_HEAD_DIMS and self.d not in _warned_head_dims:
+            _warned_head_dims.add(self.d)
+            print(f"[vllm_cpp_b200] warning: head size {self.d} has no tensor-core attention kernel "
+                  f"(those take {ops.MMA_HEAD_DIMS}); bfloat16 attention runs the plain kernel, one warp per "
+                  "token and head, many times slower", file=sys.stderr, flush=True)
 
     def step_arrays(self):
         """What the kernels need per step beyond the common arrays, built on the host from the step's
@@ -206,7 +124,7 @@ class PagedAttention(Mixer):
     def attend(self, q, attn, step, cache, block_table):
         if self._tensor_core_path():
             kw = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size,
-                      window=self.window, scale=self.scale)
+                      window=self.window, scale=self.scale, planes=self.planes)
             if step.decode_only:
                 nsplit = step.shapes.get(self._splits_key())
                 split_tiles = step.extras.get(self._splits_key())
@@ -233,4 +151,96 @@ class PagedAttention(Mixer):
             return
         ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
                            num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
-                           page_size=cache.page_size, window=self.window, scale=self.scale)
+                           page_size=cache.page_size, window=self.window, scale=self.scale, planes=self.planes)
+
+
+@register_mixer("attention")
+class PagedAttention(PagedAttentionKernels):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, out_bias: bool, window: int, position: PartSpec, dtype, device):
+        if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} heads cannot share {num_kv_heads} kv heads")
+        if head_dim <= 0 or head_dim % 2:
+            raise ValueError(f"attention: head_dim {head_dim} must be positive and even")
+        if head_dim > MAX_HEAD_DIM:
+            raise ValueError(f"attention: head_dim {head_dim} exceeds {MAX_HEAD_DIM}, the largest the kernels take")
+        if out_bias:
+            raise ValueError("attention: a bias on the output projection is not built")
+        if window < 0:
+            raise ValueError("attention: window must be 0 (all keys) or positive")
+        self.hidden, self.nh, self.nkv, self.d = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qkv_bias, self.window = bool(qkv_bias), int(window)
+        self.dtype, self.device = dtype, device
+        self.position = build_part(POSITION_ENCODINGS, "position encoding", position, dtype=dtype, device=device)
+        # 1/sqrtf(d) in float, as src/layers/attention.cpp:126 computes it
+        self.scale = float(np.float32(1.0) / np.sqrt(np.float32(head_dim)))
+        self.w_qkv = None
+        self.b_qkv = None
+        self.w_o = None
+
+    # -- tensors
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        q, kv = self.nh * self.d, self.nkv * self.d
+        specs = {"q_proj.weight": ParamSpec((q, self.hidden)),
+                 "k_proj.weight": ParamSpec((kv, self.hidden)),
+                 "v_proj.weight": ParamSpec((kv, self.hidden)),
+                 "o_proj.weight": ParamSpec((self.hidden, q))}
+        if self.qkv_bias:
+            specs.update({"q_proj.bias": ParamSpec((q,), "bias"),
+                          "k_proj.bias": ParamSpec((kv,), "bias"),
+                          "v_proj.bias": ParamSpec((kv,), "bias")})
+        for name, s in self.position.param_specs().items():
+            specs["position." + name] = s
+        return specs
+
+    def load_params(self, tensors):
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                                tensors["v_proj.weight"]], dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
+                                    tensors["v_proj.bias"]], dim=0).contiguous()
+        self.position.load_params({k[len("position."):]: v for k, v in tensors.items()
+                                   if k.startswith("position.")})
+
+        self.warn_if_plain()
+
+    # -- cache
+    def cache_spec(self):
+        return PagedKVSpec(self.nkv, self.d, self.window)
+
+    def workspace_bytes(self, n_tokens, n_reqs):
+        q = self.nh * self.d
+        return workspace_piece((n_tokens, q + 2 * self.nkv * self.d), self.dtype) + 2 * workspace_piece((n_tokens, q), self.dtype)
+
+    # -- run
+    def fuses_norm(self, n_tokens):
+        return ops.linear_fuses_norm(n_tokens, self.w_qkv) and ops.linear_fuses_norm(n_tokens, self.w_o)
+
+    def forward(self, x, out, step, cache, writes_cache, ws, x_scale=None, fuse=None):
+        n = x.shape[0]
+        mark = ws.mark()
+        qkv = ws.take((n, (self.nh + 2 * self.nkv) * self.d), self.dtype)
+        ops.linear(x, self.w_qkv, qkv, x_scale=x_scale)
+        q = ws.take((n, self.nh * self.d), self.dtype)
+        block_table = step.block_tables[cache.group]
+        fused = self.position.fused()
+        bias = self.b_qkv
+        if fused is None:
+            # An encoding the fused kernel does not know: bias first, then the
+            # encoding's own code on q and k, then the plain copy into the cache.
+            if bias is not None:
+                ops.add_bias(qkv, bias)
+                bias = None
+            q3 = qkv[:, : self.nh * self.d].unflatten(1, (self.nh, self.d))
+            k3 = qkv[:, self.nh * self.d: (self.nh + self.nkv) * self.d].unflatten(1, (self.nkv, self.d))
+            self.position.apply(q3, k3, step.positions)
+            fused = {"rotary_dim": 0, "pairing": 0, "denom": None}
+        ops.rope_cache_write(qkv, bias, step.positions, step.req_of_token, block_table, fused["denom"], q,
+                             cache.pages, num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
+                             rotary_dim=fused["rotary_dim"], pairing=fused["pairing"],
+                             page_size=cache.page_size, write_kv=writes_cache)
+        attn = ws.take((n, self.nh * self.d), self.dtype)
+        self.attend(q, attn, step, cache, block_table)
+        ops.linear(attn, self.w_o, out, fuse=fuse)
+        ws.release(mark)

@@ -35,10 +35,13 @@ class ParamSpec:
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Keys and values in pages.  ``window`` 0: all keys are kept; > 0: only the
-    last ``window`` keys are read, pages left of the window are given back."""
+    last ``window`` keys are read, pages left of the window are given back.
+    ``planes`` 2: a page holds the keys and then the values of its slots; 1: one row per slot
+    that the mixer reads as key and as value (a cached latent row, ``head_dim`` its width)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -51,7 +54,7 @@ class StateSpec:
 @dataclass
 class PagedKVView:
     """What a mixer sees of a paged cache layer."""
-    pages: torch.Tensor          # [num_pages, 2, num_kv_heads, page_size * head_dim], a block laid out as csrc/common.cuh says (kv_pos)
+    pages: torch.Tensor          # [num_pages, planes, num_kv_heads, page_size * head_dim], a block laid out as csrc/common.cuh says (kv_pos)
     group: int                   # index into StepContext.block_tables
     page_size: int
 
@@ -206,6 +209,13 @@ class Norm(Part):
         """residual += delta (float32, in place, unless rows are gathered); out = norm(residual)."""
         raise NotImplementedError
 
+    def add_normed(self, y: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
+                   residual: torch.Tensor, plain: Optional[torch.Tensor], mult: float) -> None:
+        """The norm on a sublayer's result: residual += mult * norm(y * sigmoid(gate + gate_bias)) (no gate:
+        norm(y)), in float32 in place; ``plain``, when given, receives the new rows in the compute type.
+        Arrangements that norm what a sublayer returns call this; norms that cannot do it raise."""
+        raise NotImplementedError(f"{type(self).__name__} cannot be applied to a sublayer's result")
+
     def split(self):
         """(gain, eps) if the norm is y = x * rsqrt(mean(x^2) + eps) * gain with a float32 gain vector:
         then the product before it may apply the gain and the product after it the per-row factor
@@ -232,6 +242,31 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class TokenShift(Part):
+    """Mixes every row of the residual stream with the row before it in the same request, ahead of a
+    sublayer.  The row before a step's first row is per-request state (``state_spec``)."""
+
+    def state_spec(self):
+        """StateSpec of what the part keeps per request."""
+        raise NotImplementedError
+
+    def forward(self, x: torch.Tensor, shifted: torch.Tensor, plain: Optional[torch.Tensor], step: StepContext,
+                state: StateView) -> None:
+        """x: float32 residual stream [n_tokens, hidden]; shifted (and plain, x itself in the compute type,
+        when asked for): [n_tokens, hidden] in the compute type."""
+        raise NotImplementedError
+
+
+class Gate(Part):
+    """An elementwise gate on a sublayer's result, computed from the sublayer's input.  ``forward`` leaves the
+    pre-activation; ``bias`` (float32 vector or None) and the activation are applied by the kernel that
+    consumes the gate (ops.gated_norm_residual: sigmoid)."""
+    bias: Optional[torch.Tensor] = None
+
+    def forward(self, x: torch.Tensor, pre: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     def fuses_norm(self, n_tokens: int) -> bool:
         """As Mixer.fuses_norm."""
@@ -254,7 +289,8 @@ class Block:
     SLOTS: Dict[str, str] = {"mixer": "mixer", "feed_forward": "feed_forward",
                              "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
-    def __init__(self, **parts):
+    def __init__(self, params: Optional[dict] = None, **parts):
+        self.params = dict(params or {})       # the arrangement's own constants (LayerSpec.block_params)
         missing = [n for n in self.SLOTS if n not in parts]
         extra = [n for n in parts if n not in self.SLOTS]
         if missing or extra:
@@ -270,6 +306,15 @@ class Block:
         if len(mixers) != 1:
             raise ValueError(f"{type(self).__name__} has {len(mixers)} mixers; it must say itself what its cache is")
         return mixers[0].cache_spec()
+
+    def state_spec(self):
+        """StateSpec of per-request state that the arrangement's parts keep beside the mixer's cache (the
+        previous row of a token shift), or None.  A run-order entry names the cache layer that holds it
+        (LayerCall.state); ``forward`` then receives its StateView as ``state``."""
+        specs = [p.state_spec() for p in self.parts.values() if isinstance(p, TokenShift)]
+        if len(specs) > 1:
+            raise ValueError(f"{type(self).__name__} has {len(specs)} parts with state; it must say itself what its state is")
+        return specs[0] if specs else None
 
     def step_arrays(self):
         """Per-step work lists of the arrangement itself, as Part.step_arrays (its parts are asked apart)."""
@@ -289,13 +334,14 @@ class Block:
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor, pending, step: StepContext,
                 cache, writes_cache: bool, ws: Workspace, next_block: "Optional[Block]" = None,
-                carry: Optional[torch.Tensor] = None):
+                carry: Optional[torch.Tensor] = None, state: Optional[StateView] = None):
         """Runs the layer.  ``pending`` says what ``delta`` holds: False nothing, True an addition to
         ``residual`` that has not been made yet, an ops.RowScale the pre-normed input (see
         accepts_prenormed; only given to a block that accepts it).  ``next_block`` runs after this
         one (None: the model's final norm does); ``carry`` is float32 scratch
-        [2, ops.sumsq_parts(hidden), n_tokens] that lives for the whole step.  Returns the new
-        ``pending``."""
+        [2, ops.sumsq_parts(hidden), n_tokens] that lives for the whole step; ``state`` the view of the
+        arrangement's own per-request state (only passed to one that declares a ``state_spec``).  Returns
+        the new ``pending``."""
         raise NotImplementedError
 
 
@@ -304,9 +350,12 @@ MIXERS: Dict[str, Callable] = {}
 FEED_FORWARDS: Dict[str, Callable] = {}
 NORMS: Dict[str, Callable] = {}
 POSITION_ENCODINGS: Dict[str, Callable] = {}
+TOKEN_SHIFTS: Dict[str, Callable] = {}
+GATES: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
 # family name (the values of Block.SLOTS) -> registry of the parts of that family
-FAMILIES: Dict[str, Dict[str, Callable]] = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+FAMILIES: Dict[str, Dict[str, Callable]] = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS,
+                                            "token_shift": TOKEN_SHIFTS, "gate": GATES}
 
 
 def _register(table, name):
@@ -320,6 +369,8 @@ def register_mixer(name): return _register(MIXERS, name)
 def register_feed_forward(name): return _register(FEED_FORWARDS, name)
 def register_norm(name): return _register(NORMS, name)
 def register_position_encoding(name): return _register(POSITION_ENCODINGS, name)
+def register_token_shift(name): return _register(TOKEN_SHIFTS, name)
+def register_gate(name): return _register(GATES, name)
 def register_block(name): return _register(BLOCKS, name)
 
 

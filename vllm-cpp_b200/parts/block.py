@@ -17,6 +17,7 @@ import torch
 
 from ..csrc import ops
 from .base import Block, register_block, workspace_piece
+from .mlp import NoFeedForward
 
 
 @register_block("prenorm")
@@ -62,3 +63,55 @@ class PreNormBlock(Block):
         self.feed_forward.forward(mixed, delta, step, ws, x_scale=ends.scale(), fuse=ends_layer)
         ws.release(mark)
         return ends_layer.scale()
+
+
+@register_block("shift_gate_postnorm")
+class ShiftGatePostNormBlock(Block):
+    """Sublayers that read the residual stream itself and are normed on the way back:
+
+        x += m * mixer_norm(mixer(shift(x)) * sigmoid(mixer_gate(x)))
+        x += m * feed_forward_norm(feed_forward(x) * sigmoid(feed_forward_gate(x)))
+
+    ``shift`` (a TokenShift) changes only what the mixer reads; the gates read the unshifted rows.
+    ``m`` is the arrangement's constant ``residual_mult``.  Gate, norm and addition of a sublayer are one
+    kernel (Norm.add_normed), which also hands the new rows to the next sublayer in the compute type.  A
+    layer whose feed-forward is "none" has only the first line (its gate and norm slots are "none" too).
+    The float32 path reads the residual stream directly; nothing is rounded on the way."""
+
+    SLOTS = {"shift": "token_shift", "mixer": "mixer", "mixer_gate": "gate", "mixer_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_gate": "gate", "feed_forward_norm": "norm"}
+
+    def __init__(self, params=None, **parts):
+        super().__init__(params=params, **parts)
+        self.mult = float(self.params.get("residual_mult", 1.0))
+        self.has_ff = not isinstance(self.feed_forward, NoFeedForward)
+
+    def workspace_bytes(self, n_tokens, n_reqs, hidden, dtype):
+        return 4 * workspace_piece((n_tokens, hidden), dtype) + super().workspace_bytes(n_tokens, n_reqs, hidden, dtype)
+
+    def forward(self, residual, delta, pending, step, cache, writes_cache, ws, next_block=None, carry=None, state=None):
+        if isinstance(pending, ops.RowScale):
+            raise ValueError("shift_gate_postnorm takes the residual stream as it is")
+        if pending:
+            residual.add_(delta)                  # an arrangement before this one left its last addition to its successor
+        if state is None:
+            raise ValueError("shift_gate_postnorm needs the state layer of its token shift (LayerCall.state)")
+        mark = ws.mark()
+        n, hidden = residual.shape
+        dtype = delta.dtype
+        exact = dtype == torch.float32
+        shifted = ws.take((n, hidden), dtype)
+        plain = None if exact else ws.take((n, hidden), dtype)
+        self.shift.forward(residual, shifted, plain, step, state)
+        x = residual if exact else plain
+        pre = ws.take((n, hidden), dtype)
+        y = ws.take((n, hidden), dtype)
+        self.mixer_gate.forward(x, pre)
+        self.mixer.forward(shifted, y, step, cache, writes_cache, ws)
+        self.mixer_norm.add_normed(y, pre, self.mixer_gate.bias, residual, plain if self.has_ff else None, self.mult)
+        if self.has_ff:
+            self.feed_forward_gate.forward(x, pre)
+            self.feed_forward.forward(x, y, step, ws)
+            self.feed_forward_norm.add_normed(y, pre, self.feed_forward_gate.bias, residual, None, self.mult)
+        ws.release(mark)
+        return False

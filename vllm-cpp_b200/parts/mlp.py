@@ -14,24 +14,36 @@ from ..csrc import ops
 from .base import FeedForward, ParamSpec, register_feed_forward, workspace_piece
 
 
+@register_feed_forward("none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: arrangements that allow it skip the sublayer."""
+
+    def __init__(self, dtype=None, device=None):
+        pass
+
+
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str, dtype, device):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str, dtype, device,
+                 tensor_names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation {activation!r} is not built (only 'silu')")
         self.hidden, self.inter = hidden_size, intermediate_size
+        self.names = tuple(tensor_names)          # local names of the gate, up and down matrices
         self.dtype, self.device = dtype, device
         self.w_gate_up = None     # [2*inter, hidden]
         self.w_down = None        # [hidden, inter]
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
-                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
-                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+        gate, up, down = self.names
+        return {gate: ParamSpec((self.inter, self.hidden)),
+                up: ParamSpec((self.inter, self.hidden)),
+                down: ParamSpec((self.hidden, self.inter))}
 
     def load_params(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        gate, up, down = self.names
+        self.w_gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()
+        self.w_down = tensors[down].contiguous()
 
     def product_weights(self):
         return [(self.w_gate_up, self.inter), (self.w_down, 0)]

@@ -14,13 +14,15 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..config.model_spec import ModelSpec
 from ..csrc import ops
 from .base import BLOCKS, FAMILIES, NORMS, ParamSpec, StepContext, Workspace, build_part
 # importing the modules registers the built-in parts
-from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, position as _position  # noqa: F401
+from . import (attention as _attention, block as _block, gate as _gate, latent_attention as _latent,  # noqa: F401
+               mlp as _mlp, norm as _norm, position as _position, shift as _shift)
 
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -56,9 +58,10 @@ class DecoderModel:
             if set(ls.parts) != set(arrangement.SLOTS):
                 raise ValueError(f"layer {i}: arrangement {ls.block!r} takes the parts {sorted(arrangement.SLOTS)}, "
                                  f"the layer names {sorted(ls.parts)}")
-            self.blocks.append(arrangement(**{
-                slot: build_part(FAMILIES[family], family, ls.parts[slot], **ctx)
-                for slot, family in arrangement.SLOTS.items()}))
+            built = {slot: build_part(FAMILIES[family], family, ls.parts[slot], **ctx)
+                     for slot, family in arrangement.SLOTS.items()}
+            params = getattr(ls, "block_params", None)
+            self.blocks.append(arrangement(params=params, **built) if params else arrangement(**built))
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, **ctx)
         self.embed: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
@@ -71,6 +74,8 @@ class DecoderModel:
         for call in self.spec.run_order:
             if call.writes_cache:
                 specs[call.cache] = self.blocks[call.layer].cache_spec()
+            if call.state >= 0:
+                specs[call.state] = self.blocks[call.layer].state_spec()
         return specs
 
     def _check_cache_sharing(self) -> None:
@@ -81,6 +86,10 @@ class DecoderModel:
                 if own != specs[call.cache]:
                     raise ValueError(f"run_order[{i}]: layer {call.layer} needs {own} but reads cache "
                                      f"{call.cache} of kind {specs[call.cache]}")
+            if (call.state >= 0) != (self.blocks[call.layer].state_spec() is not None):
+                raise ValueError(f"run_order[{i}]: layer {call.layer} " + (
+                    "keeps no state but is given a state layer" if call.state >= 0 else
+                    "keeps per-request state; its entry must name a cache layer for it (LayerCall.state)"))
 
     # ---------------------------------------------------------------- tensors
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -156,8 +165,9 @@ class DecoderModel:
         order = self.spec.run_order
         for i, call in enumerate(order):
             following = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            extra = {"state": caches[call.state]} if call.state >= 0 else {}
             pending = self.blocks[call.layer].forward(residual, delta, pending, step, caches[call.cache],
-                                                      call.writes_cache, ws, next_block=following, carry=carry)
+                                                      call.writes_cache, ws, next_block=following, carry=carry, **extra)
         has_delta = bool(pending)
         m = step.n_logit_rows
         out = logits[:m]
@@ -188,3 +198,25 @@ class DecoderModel:
 
 
 MODEL_CLASSES["decoder"] = DecoderModel
+
+
+@register_model_class("scaled_sinusoid_decoder")
+class ScaledSinusoidDecoderModel(DecoderModel):
+    """A decoder whose residual stream starts as  embedding * ``embedding_scale`` + a sinusoidal position
+    vector: entry 2i is sin(p f_i), entry 2i + 1 is cos(p f_i), f_i = ``position_base``^(-2i / width), p the
+    token's position in its request.  The f_i are computed once in double and rounded; the angle is their
+    float product with the position (ModelSpec.model_params gives the two constants)."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        p = spec.model_params
+        self.embedding_scale = float(p.get("embedding_scale", 1.0))
+        base = float(p.get("position_base", 10000.0))
+        i = np.arange((self.hidden + 1) // 2, dtype=np.float64)
+        self.inv_freq = torch.from_numpy(np.power(base, -2.0 * i / self.hidden).astype(np.float32)).to(device)
+
+    def tensors(self):
+        return super().tensors() + [self.inv_freq]
+
+    def embed_tokens(self, step, residual):
+        ops.embedding_sinusoid(self.embed, step.token_ids, step.positions, self.inv_freq, residual, self.embedding_scale)

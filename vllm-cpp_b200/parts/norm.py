@@ -33,3 +33,42 @@ class RMSNorm(Norm):
 
     def forward(self, residual, delta, out, row_index=None):
         ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index)
+
+    def add_normed(self, y, gate, gate_bias, residual, plain, mult):
+        ops.gated_norm_residual(y, gate, gate_bias, self.weight, residual, plain, mult, self.eps)
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm(Norm):
+    """RMSNorm whose gain is one number for all coordinates: y = x / sqrt(mean(x^2) + eps) * g.  The tensor
+    has no dimensions and the slot's name itself (local name "").  ``out_scale`` is a constant that
+    multiplies what ``forward`` returns (a model that scales its logits puts the factor here: the output
+    product is linear)."""
+
+    def __init__(self, size: int, eps: float, dtype, device, out_scale: float = 1.0):
+        if size <= 0 or not eps > 0:
+            raise ValueError(f"rmsnorm_scalar: size {size} and eps {eps} must be positive")
+        self.size, self.eps, self.out_scale = size, float(eps), float(out_scale)
+        self.gain: Optional[torch.Tensor] = None          # the number, float32 [1]
+        self.weight: Optional[torch.Tensor] = None        # gain * out_scale on every coordinate, for the vector kernel
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"": ParamSpec((), "gain")}
+
+    def load_params(self, tensors):
+        self.gain = tensors[""].reshape(1).to(torch.float32).contiguous()
+        self.weight = (self.gain * self.out_scale).expand(self.size).contiguous()
+
+    def forward(self, residual, delta, out, row_index=None):
+        ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index)
+
+    def add_normed(self, y, gate, gate_bias, residual, plain, mult):
+        ops.gated_norm_residual(y, gate, gate_bias, self.gain, residual, plain, mult * self.out_scale, self.eps)
+
+
+@register_norm("none")
+class NoNorm(Norm):
+    """Fills the norm slot of a sublayer that a layer does not have."""
+
+    def __init__(self, dtype=None, device=None):
+        pass
