@@ -175,3 +175,73 @@ def forward(cfg, w, tokens, return_layers=False):
 
 def greedy(logits_row):
     return int(np.argmax(logits_row))
+
+
+# ------------------------------------------------------- weights for tests
+def tensor_shapes(cfg):
+    """{name: shape} of every tensor a model of this configuration has."""
+    width = cfg["width"]
+    shapes = {"embed": (cfg["vocab"], width), "head": (cfg["vocab"], width), "final.norm": ()}
+    for l, layer in enumerate(cfg["layers"]):
+        p, m = f"l{l}.", layer["mixer"]
+        H, d, dv, r = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+        shapes.update({p + "shift": (width,), p + "rg1": (width, width), p + "rg1.b": (width,), p + "norm1": (),
+                       p + "mix.q": (H * d, width), p + "mix.uk": (H * d, r), p + "mix.uv": (H * dv, r),
+                       p + "mix.g": (H * dv, width), p + "mix.o": (width, H * dv)})
+        if m.get("kv_from") is None:
+            shapes.update({p + "mix.dkv": (r, width), p + "mix.dkv.norm": (r,)})
+        if layer.get("mlp") is not None:
+            ff = layer["mlp"]["ff"]
+            shapes.update({p + "rg2": (width, width), p + "rg2.b": (width,), p + "norm2": (),
+                           p + "mlp.gate": (ff, width), p + "mlp.up": (ff, width), p + "mlp.down": (width, ff)})
+    return shapes
+
+
+def random_weights(cfg, seed, sharp=1.0):
+    """Random weights with activations of order one everywhere; ``sharp`` multiplies the queries' matrices
+    so that attention is peaked and a wrong or missing key shows in the logits."""
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
+        if shape == ():
+            w[name] = np.asarray(1.0 + 0.2 * rng.standard_normal())
+        elif leaf == "shift":
+            w[name] = rng.uniform(0.0, 1.0, shape)
+        elif leaf == "mix.dkv.norm":
+            w[name] = 1.0 + 0.2 * rng.standard_normal(shape)
+        elif leaf.endswith(".b"):
+            w[name] = 0.5 * rng.standard_normal(shape)
+        elif name == "embed":
+            w[name] = rng.standard_normal(shape)
+        else:
+            w[name] = rng.standard_normal(shape) / np.sqrt(shape[-1])
+            if leaf == "mix.q":
+                w[name] *= sharp
+    return w
+
+
+def to_bf16_bits(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def write_model_folder(path, cfg, weights, store="F32"):
+    """config.json and model.safetensors with the tensors as float32 or bfloat16."""
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, off = {}, [], 0
+    for name in sorted(weights):
+        a = np.asarray(weights[name], dtype=np.float32)          # a norm's single number keeps its empty shape
+        raw = a.tobytes() if store == "F32" else to_bf16_bits(a).tobytes()
+        header[name] = {"dtype": store, "shape": list(np.shape(weights[name])), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hb = json.dumps(header).encode()
+    hb += b" " * ((8 - len(hb) % 8) % 8)
+    with open(os.path.join(path, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hb)))
+        f.write(hb)
+        for raw in blobs:
+            f.write(raw)

@@ -1,4 +1,4 @@
-// Paged attention over the cache, plain SIMT form, for any head size up to 512
+// Paged attention over the cache, plain SIMT form, for any head size up to 1024
 // and both storage types.  It is the 32-bit path's attention and the reference
 // that the tensor-core kernels are compared with.
 //
@@ -15,7 +15,7 @@
 // not kept: a row always has at least its own key.
 #include "common.cuh"
 
-#define ATT_MAX_D 512
+#define ATT_MAX_D 1024
 #define ATT_WARPS 4
 
 struct AttnArgs {
@@ -124,12 +124,12 @@ VCB_EXPORT int vcb_attention_simt_planes(const void* q, const void* cache, void*
     const int blocks = (int)((items + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    const bool wide = d > 256;          // the output row in registers: 8 floats a lane up to 256, 16 beyond
+    // the output row in registers: 8 floats a lane up to 256 elements, 32 up to 1024
     if (dtype == VCB_F32) {
-        if (wide) vcb_launch(attention_simt_kernel<float, 512>, blocks, ATT_WARPS * 32, smem, s, a);
+        if (d > 256) vcb_launch(attention_simt_kernel<float, 1024>, blocks, ATT_WARPS * 32, smem, s, a);
         else vcb_launch(attention_simt_kernel<float, 256>, blocks, ATT_WARPS * 32, smem, s, a);
     } else if (dtype == VCB_BF16) {
-        if (wide) vcb_launch(attention_simt_kernel<__nv_bfloat16, 512>, blocks, ATT_WARPS * 32, smem, s, a);
+        if (d > 256) vcb_launch(attention_simt_kernel<__nv_bfloat16, 1024>, blocks, ATT_WARPS * 32, smem, s, a);
         else vcb_launch(attention_simt_kernel<__nv_bfloat16, 256>, blocks, ATT_WARPS * 32, smem, s, a);
     } else return VCB_ERR_BAD_ARG;
     return vcb_last_error();

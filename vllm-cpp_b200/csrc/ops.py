@@ -221,7 +221,7 @@ def rope_cache_write(qkv, bias, positions, req_of_token, block_table, denom, q_o
         "rope_cache_write")
 
 
-SIMT_MAX_HEAD_DIM = 512
+SIMT_MAX_HEAD_DIM = 1024
 
 
 def attention_simt(q, cache, out, positions, req_of_token, block_table, *, num_heads: int,

@@ -137,7 +137,7 @@ class RolesunConfig:
 
 
 def rolesun_model_spec(c: RolesunConfig) -> ModelSpec:
-    layers, order = [], []
+    layers, order, absent = [], [], []
     # cache layers: first the latents of the layers that own some, in layer order, then every layer's token-shift row
     owners = [i for i, layer in enumerate(c.layers) if layer.mixer.kv_from is None]
     latent_layer = {i: k for k, i in enumerate(owners)}
@@ -163,6 +163,8 @@ def rolesun_model_spec(c: RolesunConfig) -> ModelSpec:
             names={"shift": p + "shift", "mixer": p + "mix.", "mixer_gate": p + "rg1", "mixer_norm": p + "norm1",
                    "feed_forward": p + "mlp.", "feed_forward_gate": p + "rg2", "feed_forward_norm": p + "norm2"},
         ))
+        if not has_ff:          # a file may still hold the tensors around a feed-forward that the layer does not have
+            absent += [p + "norm2", p + "rg2", p + "rg2.b"]
         order.append(LayerCall(layer=i, cache=latent_layer[source], writes_cache=m.kv_from is None, state=len(owners) + i))
     return ModelSpec(
         architecture="Rolesun",
@@ -176,6 +178,7 @@ def rolesun_model_spec(c: RolesunConfig) -> ModelSpec:
         embed_name="embed",
         final_norm_prefix="final.norm",
         lm_head_name="head",
+        ignored_tensors=absent,
         init_std=0.05,
         init_gain_std=0.05,
         model_class="scaled_sinusoid_decoder",
