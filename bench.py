@@ -430,6 +430,232 @@ def run_kernels(cfg) -> int:
     return 0
 
 
+# ------------------------------------------------------------------- the Rolesun design beside Qwen2
+# Layer sizes that resemble real models' (width, heads, head size, feed-forward width, layers measured).  Rolesun
+# with a latent of 128 and a window that holds the whole context; Qwen2 at equal width, heads, head size and
+# feed-forward width with one key/value head, the nearest it has to one cached row per token.
+ROLESUN_SIZES = {"2k": dict(width=2048, heads=16, dim=128, ff=8192, layers=8),
+                 "4k": dict(width=4096, heads=32, dim=128, ff=14336, layers=4)}
+ROLESUN_VOCAB, ROLESUN_RANK, ROLESUN_CONTEXT, ROLESUN_PROMPT = 32000, 128, 2048, 2048
+
+
+def rolesun_configs(size):
+    z = ROLESUN_SIZES[size]
+    mixer = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "kv_rank": ROLESUN_RANK, "scale": z["dim"] ** -0.5,
+             "mask": {"size": 2 * ROLESUN_CONTEXT}}
+    rolesun = {"architecture": "Rolesun", "vocab": ROLESUN_VOCAB, "width": z["width"], "residual_mult": 0.7, "logit_scale": 0.25,
+               "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+               "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": z["ff"]}}
+                          for _ in range(z["layers"])]}
+    qwen = dict(QWEN25_7B, hidden_size=z["width"], num_hidden_layers=z["layers"], num_attention_heads=z["heads"],
+                num_key_value_heads=1, head_dim=z["dim"], intermediate_size=z["ff"], vocab_size=ROLESUN_VOCAB)
+    return rolesun, qwen
+
+
+def run_rolesun(a) -> int:
+    """Prefill and decode throughput of the Rolesun design beside Qwen2 at equal layer sizes (random weights, synthetic
+    cache contents, device time by CUDA events around the engine's step function), and the design's own kernels alone
+    beside the like kernels of Qwen2's layer with their share of the measured peaks.  One JSON line."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200 import EngineConfig
+    from vllm_cpp_b200.csrc import ops
+    from vllm_cpp_b200.engine.llm_engine import Engine
+    from vllm_cpp_b200.engine.runner import StepEntry
+    peaks = load_peaks()
+    steps, warmup = max(1, a.steps), max(3, a.warmup)
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sampler.mark("decode")
+    out = {"metric": "prefill and decode tok/s of Rolesun beside Qwen2 at equal layer sizes (bf16, random weights)",
+           "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic", "sizes": {}, "peaks": peaks}
+
+    def measure(cfg, batches):
+        max_batch = max(batches)
+        ctx_room = ROLESUN_CONTEXT + steps + warmup + 64
+        pages = max_batch * (ctx_room // 16 + 1) + ROLESUN_PROMPT // 16 + 16
+        engine = Engine(EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
+                                     num_gpu_blocks=pages, max_num_seqs=max_batch, max_model_len=ctx_room,
+                                     max_num_batched_tokens=ROLESUN_PROMPT, max_tokens_per_step=ROLESUN_PROMPT))
+        runner, cache, model = engine.runner, engine.cache, engine.model
+        gen = torch.Generator(device="cuda").manual_seed(1)
+        for g in cache.paged:
+            g.pages.normal_(0.0, 0.5, generator=gen)
+        # what a decode step must read: every tensor but the embedding table (its rows are a gather), and the cache
+        weight_bytes = sum(t.numel() * t.element_size() for t in model.tensors() if t is not model.embed)
+        cache_bytes_per_token = cache.bytes_per_page(model.cache_specs(), 16, model.dtype) // 16
+        res = {"weight_gb_per_step": round(weight_bytes / 1e9, 3), "cache_bytes_per_token": cache_bytes_per_token}
+        times = []
+        for k in range(warmup + 3):
+            cache.add_request("p")
+            toks = rng.integers(0, ROLESUN_VOCAB, size=ROLESUN_PROMPT).tolist()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step([StepEntry("p", toks, [ROLESUN_PROMPT - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            cache.free_request("p")
+            if k >= warmup:
+                times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        res["prefill"] = {"tokens": ROLESUN_PROMPT, "ms": round(ms, 3), "tok_s": round(ROLESUN_PROMPT / ms * 1e3)}
+        res["decode"] = {}
+        for batch in batches:
+            temperature, uniform = torch.zeros(batch, device="cuda"), torch.zeros(batch, device="cuda")
+            ids_out = torch.empty(batch, dtype=torch.int32, device="cuda")
+            toks = rng.integers(0, ROLESUN_VOCAB, size=(steps + warmup, batch))
+            ids = [f"d{batch}_{i}" for i in range(batch)]
+            for r in ids:
+                cache.add_request(r)
+                cache.reserve(r, ROLESUN_CONTEXT)
+                cache.commit(r, ROLESUN_CONTEXT)
+
+            def one(j):
+                logits = runner.step([StepEntry(r, [int(toks[j, i])], [0]) for i, r in enumerate(ids)])
+                ops.sample(logits, temperature, uniform, ids_out)
+
+            for j in range(warmup):
+                one(j)
+            torch.cuda.synchronize()
+            before = ops.launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for j in range(warmup, warmup + steps):
+                one(j)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            bytes_ = weight_bytes + batch * (ROLESUN_CONTEXT + warmup + steps / 2) * cache_bytes_per_token
+            res["decode"][str(batch)] = {"ms_per_step": round(ms, 4), "tok_s": round(batch / ms * 1e3),
+                                         "of_hbm_peak": round(bytes_ / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3),
+                                         "launches_per_step": (ops.launch_count() - before) // steps}
+            for r in ids:
+                cache.free_request(r)
+        ops.check_status()
+        del engine, runner, cache, model
+        torch.cuda.empty_cache()
+        return res
+
+    for size in (a.rolesun.split(",") if a.rolesun != "all" else sorted(ROLESUN_SIZES)):
+        rolesun, qwen = rolesun_configs(size)
+        out["sizes"][size] = {"layers": ROLESUN_SIZES[size], "rolesun": measure(rolesun, (8, 64)), "qwen2_one_kv_head": measure(qwen, (8, 64))}
+    out["kernels"] = rolesun_kernels(ROLESUN_SIZES["4k"], peaks)
+    clocks = sampler.stop()
+    out["clocks"] = clocks
+    big = out["sizes"].get("4k") or next(iter(out["sizes"].values()))
+    out.update(value=big["rolesun"]["decode"]["8"]["tok_s"], unit="tokens/s (Rolesun, 4k-wide layers, batch 8)",
+               higher_is_better=True, gpu_launches=big["rolesun"]["decode"]["8"]["launches_per_step"] * steps,
+               config={"sizes": ROLESUN_SIZES, "latent": ROLESUN_RANK, "context": ROLESUN_CONTEXT, "prompt": ROLESUN_PROMPT,
+                       "l2": "a step's weights exceed the 126 MB of L2"})
+    print(json.dumps(out))
+    return 0
+
+
+def rolesun_kernels(z, peaks):
+    """The design's own kernels alone at one layer size, each beside the like kernel of Qwen2's layer:
+    [{kernel, us, GB/s or TFLOP/s, share of the measured peak}, ...] (CUDA graphs on rotating buffers)."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.config.model_spec import PartSpec
+    from vllm_cpp_b200.csrc import ops
+    from vllm_cpp_b200.engine.runner import HostStep
+    from vllm_cpp_b200.parts.attention import PagedAttention
+    h, nh, d, r, page, bf, dev = z["width"], z["heads"], z["dim"], ROLESUN_RANK, 16, torch.bfloat16, "cuda"
+    rows = []
+
+    def rnd(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, device=dev) * scale).to(dtype)
+
+    def add(name, like, fn, copies, bytes_=0, flops=0):
+        us = ops.time_in_graph(fn, reps=max(4, copies))
+        rate = bytes_ / us / 1e3 if bytes_ else flops / us / 1e6
+        rows.append({"kernel": name, "like": like, "us": round(us, 2), ("gb_s" if bytes_ else "tflop_s"): round(rate, 1),
+                     "of_peak": round(rate / (peaks["hbm_gbs"] if bytes_ else peaks["bf16_tflops"]), 3)})
+
+    for t in (64, 2048):
+        c = 6 if t == 64 else 3
+        x = [rnd(t, h, dtype=torch.float32) for _ in range(c)]
+        y, g, o1, o2 = ([rnd(t, h) for _ in range(c)] for _ in range(4))
+        mu, bias, one, gain = torch.rand(h, device=dev), torch.zeros(h, device=dev), torch.ones(1, device=dev), torch.ones(h, device=dev)
+        state = torch.zeros(1, h, device=dev)
+        q_start = torch.tensor([0, t], dtype=torch.int32, device=dev)
+        req, pos, slots = torch.zeros(t, dtype=torch.int32, device=dev), torch.arange(t, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+        add(f"token shift, {t} tokens", "", lambda i: ops.token_shift(x[i % c], mu, state, o1[i % c], o2[i % c], q_start, req, pos, slots), c, bytes_=t * h * 8)
+        add(f"gate + norm + residual, {t} tokens", "", lambda i: ops.gated_norm_residual(y[i % c], g[i % c], bias, one, x[i % c], o1[i % c], 0.7, 1e-6), c,
+            bytes_=t * h * 14)
+        add(f"Qwen2: residual add + RMSNorm, {t} tokens", "like the two above", lambda i: ops.add_rmsnorm(x[i % c], y[i % c], gain, o1[i % c], 1e-6), c, bytes_=t * h * 12)
+        width = nh * d + r + nh * d
+        proj = [rnd(t, width) for _ in range(c)]
+        n_pages = t // page + 2
+        lat = torch.zeros(n_pages, page * r, dtype=bf, device=dev)
+        bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        gr = torch.ones(r, device=dev)
+        add(f"latent norm + cache write, {t} tokens", "", lambda i: ops.latent_cache_write(proj[i % c][:, nh * d: nh * d + r], gr, pos, req, bt, lat, page_size=page, eps=1e-6),
+            c, bytes_=t * r * 4)
+        qw = (nh + 2) * d
+        qkv, q_out = [rnd(t, qw) for _ in range(c)], torch.empty(t, nh * d, dtype=bf, device=dev)
+        kvc = torch.zeros(n_pages, 2, 1, page * d, dtype=bf, device=dev)
+        denom = torch.from_numpy(np.power(np.float32(1e6), np.arange(d // 2, dtype=np.float32) * 2 / d).astype(np.float32)).to(dev)
+        qb = torch.zeros(qw, device=dev)
+        add(f"Qwen2: q/k/v bias + rotation + cache write, {t} tokens", "like the one above (it also moves q)",
+            lambda i: ops.rope_cache_write(qkv[i % c], qb, pos, req, bt, denom, q_out, kvc, num_heads=nh, num_kv_heads=1, head_dim=d, rotary_dim=d,
+                                           pairing=0, page_size=page, write_kv=True), c, bytes_=t * qw * 4)
+        wk = [rnd(nh, r, d, scale=0.05) for _ in range(6)]
+        ql = torch.empty(t, nh * r, dtype=bf, device=dev)
+        kind = dict(bytes_=nh * r * d * 2) if t <= ops.HEADWISE_LIBRARY_TOKENS else dict(flops=2.0 * t * nh * r * d)
+        add(f"queries into the latent space (per head), {t} tokens", "", lambda i: ops.headwise_linear(proj[i % c][:, : nh * d], wk[i % 6], ql), 6, **kind)
+        wv = [rnd(nh, d, r, scale=0.05) for _ in range(6)]
+        ol, og = rnd(t, nh * r), torch.empty(t, nh * d, dtype=bf, device=dev)
+        add(f"result out of the latent space + output gate (per head), {t} tokens", "",
+            lambda i: ops.headwise_linear(ol, wv[i % 6], og, gate=proj[i % c][:, nh * d + r:]), 6, **kind)
+        wd = [rnd(nh * d, nh * d, scale=0.02) for _ in range(6)]
+        for w in wd:
+            ops.tile_weights(w)
+        xo, oo = rnd(t, nh * d), torch.empty(t, nh * d, dtype=bf, device=dev)
+        if t <= 128:
+            add(f"Qwen2: a dense product of the same width [{nh * d} x {nh * d}], {t} tokens (tcgen05)", "like the two above, 32x their weights",
+                lambda i: ops.gemm_bf16_tcgen05(xo, wd[i % 6], oo), 6, bytes_=nh * d * nh * d * 2)
+        else:
+            add(f"Qwen2: a dense product of the same width, {t} tokens (cuBLAS)", "like the two above, 32x their work",
+                lambda i: ops._library_mm(xo, wd[i % 6], oo), 6, flops=2.0 * t * nh * d * nh * d)
+    # prefill attention: one prompt
+    t = 2048
+    n_pages = t // page + 2
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+    q_start, ctx = torch.tensor([0, t], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    n_tiles = -(-t * nh // ops.TC_ATTENTION_TILE_ROWS)
+    tile_req = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
+    tile_row0 = torch.from_numpy((np.arange(n_tiles, dtype=np.int32) * ops.TC_ATTENTION_TILE_ROWS)[::-1].copy()).to(dev)
+    q, o = rnd(t, nh * r), torch.empty(t, nh * r, dtype=bf, device=dev)
+    for planes, name, like in ((1, "attention over latent rows, prompt of 2,048", ""), (2, "Qwen2: attention, one kv head, prompt of 2,048", "like the one above")):
+        kv = rnd(n_pages, planes, 1, page * r, scale=0.5)
+        add(name, like, lambda i: ops.attention_prefill_tc(q, kv, o, q_start, ctx, bt, tile_req, tile_row0, num_heads=nh, num_kv_heads=1, head_dim=r,
+                                                           page_size=page, window=0, scale=d ** -0.5, planes=planes), 4, flops=4.0 * nh * r * t * (t + 1) / 2)
+    # decode attention
+    part = PagedAttention(h, nh, 1, r, True, False, 0, PartSpec("none"), bf, dev)
+    for batch in (8, 64):
+        contexts = [ROLESUN_CONTEXT - 1] * batch
+        blocks = -(-ROLESUN_CONTEXT // page)
+        bt = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
+        q_start, ctx = torch.arange(batch + 1, dtype=torch.int32, device=dev), torch.tensor(contexts, dtype=torch.int32, device=dev)
+        host = HostStep([1] * batch, contexts, page)
+        split_tiles = torch.from_numpy(part.step_arrays()[part._splits_key()](host)).to(dev)
+        nsplit = host.shapes[part._splits_key()]
+        need = batch * nh * nsplit
+        po, pml, tickets = torch.empty(need * r, device=dev), torch.empty(need * 2, device=dev), torch.zeros(batch, dtype=torch.int32, device=dev)
+        q, o = rnd(batch, nh * r), torch.empty(batch, nh * r, dtype=bf, device=dev)
+        for planes, name, like in ((1, f"attention over latent rows, decode, batch {batch}, contexts of {ROLESUN_CONTEXT}", ""),
+                                   (2, f"Qwen2: attention, one kv head, decode, batch {batch}", "like the one above")):
+            kv = rnd(batch * blocks + 1, planes, 1, page * r, scale=0.5)
+            add(name, like, lambda i: ops.attention_decode_mma(q, kv, o, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh, num_kv_heads=1,
+                                                               head_dim=r, page_size=page, window=0, scale=d ** -0.5, split_tiles=split_tiles, planes=planes),
+                4, bytes_=batch * ROLESUN_CONTEXT * planes * r * 2)
+    ops.check_status()
+    return rows
+
+
 # ------------------------------------------------------------------------------------------ reference arm
 REFERENCE_NOTES = ("the reference's own faults at these sizes, none of which changes the work of a step: an untied lm_head is "
                    "copied over the embedding table (src/model/qwen.cpp:279-281); the bias area of 3*1024 floats a layer "
@@ -577,6 +803,10 @@ def main() -> int:
     ap.add_argument("--reference-budget-s", type=float, default=1300.0,
                     help="--impl reference: begin no further measurement after this many seconds")
     ap.add_argument("--reference-b64", action="store_true", help="--impl reference: measure batch 64 too (many minutes)")
+    ap.add_argument("--rolesun", default="", metavar="SIZES",
+                    help="instead of the benchmark's workload: prefill and decode throughput of the Rolesun design beside Qwen2 "
+                         f"at equal layer sizes ({','.join(sorted(ROLESUN_SIZES))} or 'all'), and the design's kernels alone "
+                         "beside the like kernels of Qwen2's layer")
     a = ap.parse_args()
     if a.contexts:
         CONTEXT_START, CONTEXT = (int(v) for v in a.contexts.split(","))
@@ -608,6 +838,8 @@ def main() -> int:
         ops.set_pdl(False)
     if a.library_gemm:
         ops.set_tcgen05_linear(False)
+    if a.rolesun:
+        return run_rolesun(a)
     if a.mix:
         return run_mix(cfg, a)
     if a.kernels:

@@ -382,9 +382,9 @@ def test_attention_refuses_what_it_cannot_do(ops):
     with pytest.raises(ops.KernelError, match="head sizes"):
         ops.attention_prefill_tc(q, cache, q, z, z, z.view(1, 4), z[:1], z[:1], num_heads=2, num_kv_heads=2,
                                   head_dim=80, page_size=16, window=0, scale=1.0)
-    with pytest.raises(ops.KernelError, match="256"):
-        ops.attention_simt(torch.zeros((1, 272), dtype=torch.float32, device="cuda"), cache.float(), q.float(), z[:1],
-                           z[:1], z.view(1, 4), num_heads=1, num_kv_heads=1, head_dim=272, page_size=16, window=0, scale=1.0)
+    with pytest.raises(ops.KernelError, match="1024"):
+        ops.attention_simt(torch.zeros((1, 1040), dtype=torch.float32, device="cuda"), cache.float(), q.float(), z[:1],
+                           z[:1], z.view(1, 4), num_heads=1, num_kv_heads=1, head_dim=1040, page_size=16, window=0, scale=1.0)
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 1, 1), (7, 130, 33), (64, 64, 16), (200, 301, 96), (3, 1000, 513)])

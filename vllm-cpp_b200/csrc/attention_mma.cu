@@ -323,10 +323,12 @@ attention_decode_kernel(MmaAttnArgs a) {
                 const int st = it % STAGES;
                 if (!waited && (tile + 1) * BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's row
                 if (!cx_mbar_wait(empty0 + 8 * st, ((it / STAGES) & 1) ^ 1)) gave_up = true;
-                if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, 2 * TILE_BYTES);
+                // one plane of rows that are key and value at once: the tile is fetched once and read as both
+                if (lane == 0) cx_mbar_expect_tx(full0 + 8 * st, a.planes == 1 ? TILE_BYTES : 2 * TILE_BYTES);
                 __syncwarp();
                 produce_tile<D, BN>(s_tiles + st * 2 * TILE_BYTES, s_tiles + st * 2 * TILE_BYTES + TILE_BYTES,
-                                    full0 + 8 * st, tile * BN, lo, hi, pw, a.cache, head_base, page_stride, v_off, pd, lane);
+                                    full0 + 8 * st, tile * BN, lo, hi, pw, a.cache, head_base, page_stride, v_off, pd, lane,
+                                    0, a.planes == 1 ? 1 : 0);
             }
             if (pw.bad && a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
         } else {
@@ -335,7 +337,7 @@ attention_decode_kernel(MmaAttnArgs a) {
             for (int tile = my0; tile < my1; ++tile, ++it) {
                 const int st = it % STAGES;
                 if (!cx_mbar_wait(full0 + 8 * st, (it / STAGES) & 1)) gave_up = true;
-                const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
+                const uint32_t sk = s_tiles + st * 2 * TILE_BYTES, sv = a.planes == 1 ? sk : sk + TILE_BYTES;
                 const int kb = tile * BN + warp * 16;    // this warp's 16 keys
                 float s[2][4];
 #pragma unroll
