@@ -129,11 +129,14 @@ def test_gate_norm_and_residual_addition(dtype, vector_gain, gated):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n", [5, 200])
-def test_headwise_products(dtype, n):
+@pytest.mark.parametrize("n", [5, 70, 200])
+@pytest.mark.parametrize("N,K", [(40, 24), (40, 32), (136, 80)])
+def test_headwise_products(dtype, n, N, K):
+    """Both kernels (the plain one; tensor cores for short bfloat16 steps when K is a multiple of 16) and the
+    library's batched product for long bfloat16 portions."""
     from vllm_cpp_b200.csrc import ops
     rng = np.random.default_rng(3)
-    heads, N, K = 3, 40, 24
+    heads = 3
     x = stored(rng.standard_normal((n, heads * K + 8)), dtype)                         # a column slice of wider rows
     w = stored(rng.standard_normal((heads, N, K)) / 5, dtype)
     g = stored(rng.standard_normal((n, heads * N)), dtype)

@@ -70,18 +70,20 @@ VCB_EXPORT int vcb_latent_cache_write(const void* raw, int ld, const float* gain
 // out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]   (w: [heads, N, K] contiguous; x rows ldx apart with head h
 // at column h * K + x0; out rows ldo apart with head h at column h * N), float accumulation.
 // gate (may be null; rows ldg apart, head h at column h * N): out *= sigmoid(gate).
-// 64 x 64 output tile per CTA and head, 16-deep k slices in shared memory, a 4 x 4 register tile per thread,
+// 64 x 64 output tile per CTA and head, 32-deep k slices in shared memory, a 4 x 4 register tile per thread,
 // every edge guarded.  With few tokens the weights are read once and the kernel runs at the rate they
 // stream at; long portions in bfloat16 go to the library's batched product instead (ops.headwise_linear).
 #define HT 64
-#define HK 16
+#define HK 32
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 headwise_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, const T* __restrict__ gate,
                        int M, int N, int K, int ldx, int ldo, int ldg) {
-    __shared__ float As[HK][HT + 1];
-    __shared__ float Ws[HK][HT + 1];
+    // rows 68 floats apart: a thread's four values of a k are one 16-byte load (the loop is bound by shared-memory
+    // loads, not by the multiplications)
+    __shared__ __align__(16) float As[HK][HT + 4];
+    __shared__ __align__(16) float Ws[HK][HT + 4];
     pdl_start();
     const int h = blockIdx.z;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -93,23 +95,33 @@ headwise_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __re
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    // a slice is 64 rows x 32 k per operand, 8 elements a thread; the next slice is fetched into registers
+    // while this one is multiplied, so a global load's latency is paid once, not once per slice
+    float pa[8], pw[8];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int idx = threadIdx.x + e * 256;
+            const int r = idx / HK, k = k0 + idx % HK;
+            pa[e] = (m0 + r < M && k < K) ? to_f32<T>(xh[(size_t)(m0 + r) * ldx + k]) : 0.0f;
+            pw[e] = (n0 + r < N && k < K) ? to_f32<T>(wh[(size_t)(n0 + r) * K + k]) : 0.0f;
+        }
+    };
+    fetch(0);
     for (int k0 = 0; k0 < K; k0 += HK) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 8; ++e) {
             const int idx = threadIdx.x + e * 256;
-            const int r = idx / HK, kk = idx % HK;
-            const int k = k0 + kk;
-            As[kk][r] = (m0 + r < M && k < K) ? to_f32<T>(xh[(size_t)(m0 + r) * ldx + k]) : 0.0f;
-            Ws[kk][r] = (n0 + r < N && k < K) ? to_f32<T>(wh[(size_t)(n0 + r) * K + k]) : 0.0f;
+            As[idx % HK][idx / HK] = pa[e];
+            Ws[idx % HK][idx / HK] = pw[e];
         }
         __syncthreads();
+        if (k0 + HK < K) fetch(k0 + HK);
 #pragma unroll
         for (int kk = 0; kk < HK; ++kk) {
-            float av[4], wv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) wv[j] = Ws[kk][tx * 4 + j];
+            const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 w4 = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, wv[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -132,13 +144,84 @@ headwise_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __re
     }
 }
 
+// The same product on tensor cores for bfloat16 steps of few tokens (mma.sync m16n8k16, float accumulation): a warp
+// owns 16 tokens x 32 features of one head and walks K in steps of 16, its fragments loaded straight from global
+// memory as 32-bit pairs (both operands have K innermost, which is the layout the instruction's row x col form wants;
+// the operands of a step of few tokens are small and stay in L1/L2).  K a multiple of 16, N of 8, even strides.
+#define HW_WARPS 2
+__device__ __forceinline__ void hw_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(HW_WARPS * 32)
+headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                           __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate,
+                           int M, int N, int K, int ldx, int ldo, int ldg) {
+    pdl_start();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.z;
+    const int m0 = blockIdx.y * 16, n0 = (blockIdx.x * HW_WARPS + warp) * 32;
+    if (n0 >= N) return;
+    const int qr = lane >> 2, qc = (lane & 3) * 2;
+    const __nv_bfloat16* xa = x + (size_t)h * K + (size_t)(m0 + qr) * ldx + qc;        // rows qr and qr + 8 of the token tile
+    const bool ra = m0 + qr < M, rb = m0 + qr + 8 < M;
+    const __nv_bfloat16* wb = w + ((size_t)h * N + n0 + qr) * K + qc;                  // feature n0 + 8 * j + qr
+    bool nb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) nb[j] = n0 + 8 * j + qr < N;
+    float acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+#pragma unroll 4
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        uint32_t a[4], b[4][2];
+        a[0] = ra ? *reinterpret_cast<const uint32_t*>(xa + k0) : 0u;
+        a[1] = rb ? *reinterpret_cast<const uint32_t*>(xa + (size_t)8 * ldx + k0) : 0u;
+        a[2] = ra ? *reinterpret_cast<const uint32_t*>(xa + k0 + 8) : 0u;
+        a[3] = rb ? *reinterpret_cast<const uint32_t*>(xa + (size_t)8 * ldx + k0 + 8) : 0u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            b[j][0] = nb[j] ? *reinterpret_cast<const uint32_t*>(wb + (size_t)8 * j * K + k0) : 0u;
+            b[j][1] = nb[j] ? *reinterpret_cast<const uint32_t*>(wb + (size_t)8 * j * K + k0 + 8) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) hw_mma(acc[j], a, b[j][0], b[j][1]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int n = n0 + 8 * j + qc;
+        if (n >= N) continue;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = m0 + qr + 8 * half;
+            if (m >= M) continue;
+            float v0 = acc[j][2 * half], v1 = acc[j][2 * half + 1];
+            if (gate) {
+                const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)m * ldg + (size_t)h * N + n));
+                v0 *= 1.0f / (1.0f + expf(-g.x));
+                v1 *= 1.0f / (1.0f + expf(-g.y));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)m * ldo + (size_t)h * N + n) = __floats2bfloat162_rn(v0, v1);
+        }
+    }
+}
+
 VCB_EXPORT int vcb_headwise_linear(const void* x, const void* w, void* out, const void* gate, int M, int heads, int N,
                                    int K, int ldx, int ldo, int ldg, int dtype, void* stream) {
     if (M <= 0 || heads <= 0 || N <= 0) return 0;
     if (K <= 0 || ldx < heads * K || ldo < heads * N || (gate && ldg < heads * N) || heads > 65535) return VCB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const uintptr_t addrs = (uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)gate;
+    if (dtype == VCB_BF16 && K % 16 == 0 && N % 8 == 0 && !(addrs & 3) && !((ldx | ldo | ldg) & 1) && (M + 15) / 16 <= 65535) {
+        dim3 mgrid((N + 32 * HW_WARPS - 1) / (32 * HW_WARPS), (M + 15) / 16, heads);
+        vcb_launch(headwise_linear_mma_kernel, mgrid, HW_WARPS * 32, 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                   (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, M, N, K, ldx, ldo, ldg);
+        return vcb_last_error();
+    }
     dim3 grid((N + HT - 1) / HT, (M + HT - 1) / HT, heads);
     if (grid.y > 65535) return VCB_ERR_UNSUPPORTED;
-    cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_F32)
         vcb_launch(headwise_linear_kernel<float>, grid, 256, 0, s, (const float*)x, (const float*)w, (float*)out,
                    (const float*)gate, M, N, K, ldx, ldo, ldg);
@@ -163,12 +246,40 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ out, const T* __restrict__ g
     }
 }
 
+// bfloat16 rows of a multiple of 8 columns, 16-byte aligned: eight elements a thread.
+__global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate, int n,
+                                           int cols, int ldo, int ldg) {
+    pdl_start();
+    const int nvec = cols >> 3;
+    const long long total = (long long)n * nvec;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / nvec;
+        const int i = (int)(idx - t * nvec) * 8;
+        uint4 ov = *reinterpret_cast<const uint4*>(out + t * ldo + i);
+        const uint4 gv = *reinterpret_cast<const uint4*>(gate + t * ldg + i);
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 o = __bfloat1622float2(o2[e]), g = __bfloat1622float2(g2[e]);
+            o2[e] = __floats2bfloat162_rn(o.x * (1.0f / (1.0f + expf(-g.x))), o.y * (1.0f / (1.0f + expf(-g.y))));
+        }
+        *reinterpret_cast<uint4*>(out + t * ldo + i) = ov;
+    }
+}
+
 VCB_EXPORT int vcb_sigmoid_gate(void* out, const void* gate, int n, int cols, int ldo, int ldg, int dtype, void* stream) {
     if (n <= 0 || cols <= 0) return 0;
     if (ldo < cols || ldg < cols) return VCB_ERR_BAD_ARG;
     const size_t total = (size_t)n * cols;
     const int blocks = (int)((total + 255) / 256 < (size_t)vcb_sm_count() * 8 ? (total + 255) / 256 : (size_t)vcb_sm_count() * 8);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_BF16 && cols % 8 == 0 && ldo % 8 == 0 && ldg % 8 == 0 && !(((uintptr_t)out | (uintptr_t)gate) & 15)) {
+        const long long want = ((long long)n * (cols / 8) + 255) / 256, cap = (long long)vcb_sm_count() * 16;
+        vcb_launch(sigmoid_gate_bf16x8_kernel, (int)(want < cap ? want : cap), 256, 0, s, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)gate, n, cols, ldo, ldg);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32)
         vcb_launch(sigmoid_gate_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate, n, cols, ldo, ldg);
     else if (dtype == VCB_BF16)

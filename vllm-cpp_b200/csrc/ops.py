@@ -832,7 +832,7 @@ def headwise_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: O
     if x.dtype == torch.bfloat16 and n > HEADWISE_LIBRARY_TOKENS:
         xh = x.unflatten(1, (heads, K)).transpose(0, 1)             # [heads, n, K]
         oh = out.unflatten(1, (heads, N)).transpose(0, 1)           # [heads, n, N]
-        oh.copy_(torch.bmm(xh, w.transpose(1, 2)))
+        torch.bmm(xh, w.transpose(1, 2), out=oh)                    # the library writes the strided rows itself
         if gate is not None:
             _check(lib().vcb_sigmoid_gate(out.data_ptr(), gate.data_ptr(), n, heads * N, out.stride(0), gate.stride(0),
                                           dtype_code(out.dtype), _stream()), "sigmoid_gate")

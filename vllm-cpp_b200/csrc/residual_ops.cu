@@ -82,6 +82,53 @@ __global__ void token_shift_kernel(const float* __restrict__ x, const float* __r
     }
 }
 
+// The same for bfloat16 rows of a multiple of 8 elements: one thread per 8 elements (two 16-byte loads of x and of
+// the row before, 16-byte stores), any number of rows a CTA.
+__global__ void token_shift_bf16x8_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ state,
+                                          __nv_bfloat16* __restrict__ shifted, __nv_bfloat16* __restrict__ plain,
+                                          const int* __restrict__ q_start, const int* __restrict__ req_of_token,
+                                          const int* __restrict__ positions, const int* __restrict__ state_slots,
+                                          int n_tokens, int hidden) {
+    pdl_start();
+    const int nvec = hidden >> 3;
+    const long long total = (long long)n_tokens * nvec;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / nvec), i = (int)(idx - (long long)t * nvec) * 8;
+        const int r = req_of_token[t];
+        const int first_row = q_start[r];
+        const bool first = t == first_row;
+        float* slot = state + (size_t)state_slots[r] * hidden + i;
+        const float* cur = x + (size_t)t * hidden + i;
+        const float4 c0 = *reinterpret_cast<const float4*>(cur), c1 = *reinterpret_cast<const float4*>(cur + 4);
+        float4 p0 = make_float4(0.f, 0.f, 0.f, 0.f), p1 = p0;
+        if (!(first && positions[t] == 0)) {
+            const float* prev = first ? slot : cur - hidden;
+            p0 = *reinterpret_cast<const float4*>(prev);
+            p1 = *reinterpret_cast<const float4*>(prev + 4);
+        }
+        if (first) {
+            const float* last = x + (size_t)(q_start[r + 1] - 1) * hidden + i;
+            const float4 l0 = *reinterpret_cast<const float4*>(last), l1 = *reinterpret_cast<const float4*>(last + 4);
+            *reinterpret_cast<float4*>(slot) = l0;
+            *reinterpret_cast<float4*>(slot + 4) = l1;
+        }
+        const float4 m0 = *reinterpret_cast<const float4*>(mu + i), m1 = *reinterpret_cast<const float4*>(mu + i + 4);
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        const float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        uint4 sv, pv;
+        __nv_bfloat162* s2 = reinterpret_cast<__nv_bfloat162*>(&sv);
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            s2[e] = __floats2bfloat162_rn(c[2 * e] + (p[2 * e] - c[2 * e]) * m[2 * e], c[2 * e + 1] + (p[2 * e + 1] - c[2 * e + 1]) * m[2 * e + 1]);
+            p2[e] = __floats2bfloat162_rn(c[2 * e], c[2 * e + 1]);
+        }
+        *reinterpret_cast<uint4*>(shifted + (size_t)t * hidden + i) = sv;
+        if (plain) *reinterpret_cast<uint4*>(plain + (size_t)t * hidden + i) = pv;
+    }
+}
+
 VCB_EXPORT int vcb_token_shift(const float* x, const float* mu, float* state, void* shifted, void* plain,
                                const int* q_start, const int* req_of_token, const int* positions,
                                const int* state_slots, int n_tokens, int hidden, int dtype, void* stream) {
@@ -89,6 +136,14 @@ VCB_EXPORT int vcb_token_shift(const float* x, const float* mu, float* state, vo
     if (hidden <= 0 || !state || !shifted) return VCB_ERR_BAD_ARG;
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
+    const uintptr_t addrs = (uintptr_t)x | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)shifted | (uintptr_t)plain;
+    if (dtype == VCB_BF16 && hidden % 8 == 0 && !(addrs & 15)) {
+        const long long total = (long long)n_tokens * (hidden / 8);
+        const long long want = (total + 255) / 256, cap = (long long)vcb_sm_count() * 16;
+        vcb_launch(token_shift_bf16x8_kernel, (int)(want < cap ? want : cap), 256, 0, s, x, mu, state, (__nv_bfloat16*)shifted,
+                   (__nv_bfloat16*)plain, q_start, req_of_token, positions, state_slots, n_tokens, hidden);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32)
         vcb_launch(token_shift_kernel<float>, n_tokens, threads, 0, s, x, mu, state, (float*)shifted, (float*)plain, q_start,
                    req_of_token, positions, state_slots, hidden);
@@ -140,6 +195,75 @@ __global__ void gated_norm_residual_kernel(const T* __restrict__ y, const T* __r
     }
 }
 
+// The same for bfloat16 rows of a multiple of 8 elements that fit the CTA's registers: NCH vectors of 8 elements a
+// thread, 16-byte accesses, z kept between the two passes.
+template <int NCH>
+__global__ void gated_norm_residual_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ a,
+                                                  const float* __restrict__ b, const float* __restrict__ gain, int gain_stride,
+                                                  float* __restrict__ x, __nv_bfloat16* __restrict__ plain, int hidden,
+                                                  float mult, float eps) {
+    __shared__ float scratch[33];
+    pdl_start();
+    const size_t row = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden >> 3;
+    float z[NCH][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            const uint4 yv = *reinterpret_cast<const uint4*>(y + row + (size_t)i * 8);
+            const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&yv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(y2[e]);
+                z[c][2 * e] = f.x;
+                z[c][2 * e + 1] = f.y;
+            }
+            if (a) {
+                const uint4 av = *reinterpret_cast<const uint4*>(a + row + (size_t)i * 8);
+                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+                float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (b) {
+                    const float4 b0 = *reinterpret_cast<const float4*>(b + i * 8), b1 = *reinterpret_cast<const float4*>(b + i * 8 + 4);
+                    bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(a2[e]);
+                    z[c][2 * e] *= 1.0f / (1.0f + expf(-(f.x + bb[2 * e])));
+                    z[c][2 * e + 1] *= 1.0f / (1.0f + expf(-(f.y + bb[2 * e + 1])));
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += z[c][e] * z[c][e];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+    const float g0 = gain[0];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            float* xr = x + row + (size_t)i * 8;
+            const float4 x0 = *reinterpret_cast<const float4*>(xr), x1 = *reinterpret_cast<const float4*>(xr + 4);
+            float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += mult * ((z[c][e] * r) * (gain_stride ? gain[i * 8 + e] : g0));
+            *reinterpret_cast<float4*>(xr) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(xr + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            if (plain) {
+                uint4 pv;
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                *reinterpret_cast<uint4*>(plain + row + (size_t)i * 8) = pv;
+            }
+        }
+    }
+}
+
 VCB_EXPORT int vcb_gated_norm_residual(const void* y, const void* a, const float* b, const float* gain, int gain_stride,
                                        float* x, void* plain, int n_tokens, int hidden, float mult, float eps,
                                        int dtype, void* stream) {
@@ -147,6 +271,18 @@ VCB_EXPORT int vcb_gated_norm_residual(const void* y, const void* a, const float
     if (hidden <= 0 || !y || !gain || !x || (gain_stride != 0 && gain_stride != 1)) return VCB_ERR_BAD_ARG;
     const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
+    const uintptr_t addrs = (uintptr_t)y | (uintptr_t)a | (uintptr_t)b | (uintptr_t)x | (uintptr_t)plain | (gain_stride ? (uintptr_t)gain : 0);
+    if (dtype == VCB_BF16 && hidden % 8 == 0 && hidden / 8 <= 4 * 256 && !(addrs & 15)) {
+        const int nvec = hidden / 8;
+        const int vt = nvec >= 256 ? 256 : (nvec + 31) / 32 * 32;
+        const int nch = (nvec + vt - 1) / vt;
+        const __nv_bfloat16 *yb = (const __nv_bfloat16*)y, *ab = (const __nv_bfloat16*)a;
+        __nv_bfloat16* pb = (__nv_bfloat16*)plain;
+        if (nch == 1) vcb_launch(gated_norm_residual_bf16x8_kernel<1>, n_tokens, vt, 0, s, yb, ab, b, gain, gain_stride, x, pb, hidden, mult, eps);
+        else if (nch == 2) vcb_launch(gated_norm_residual_bf16x8_kernel<2>, n_tokens, vt, 0, s, yb, ab, b, gain, gain_stride, x, pb, hidden, mult, eps);
+        else vcb_launch(gated_norm_residual_bf16x8_kernel<4>, n_tokens, vt, 0, s, yb, ab, b, gain, gain_stride, x, pb, hidden, mult, eps);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32)
         vcb_launch(gated_norm_residual_kernel<float>, n_tokens, threads, 0, s, (const float*)y, (const float*)a, b, gain,
                    gain_stride, x, (float*)plain, hidden, mult, eps);
