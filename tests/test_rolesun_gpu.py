@@ -329,3 +329,75 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
             gap = (logits[best] - logits[tok]) / np.abs(logits).max()
             assert tok == best or gap < (1e-3 if dtype == "float32" else 5e-2), (dtype, len(p), tok, best, gap)
             seq.append(tok)
+
+
+def random_rolesun_config(rng):
+    """Sizes with odd factors everywhere: widths that are no multiple of 8 or 4, ranks of any width, up to 9 heads,
+    value sizes unlike the key sizes, layers with and without feed-forward, layers that read earlier layers' latents
+    through windows of their own."""
+    width = int(rng.choice([36, 50, 64, 90, 104, 136]))
+    layers, owners = [], []
+    for i in range(int(rng.integers(1, 6))):
+        share = owners and rng.random() < 0.4
+        src = int(rng.choice(owners)) if share else None
+        rank = layers[src][0]["kv_rank"] if share else int(rng.choice([18, 36, 64, 96, 128, 200]))
+        m = mixer(int(rng.integers(1, 10)), int(rng.choice([4, 6, 8, 16, 20])), int(rng.choice([3, 8, 12, 16])), rank,
+                  int(rng.integers(1, 90)), scale=float(rng.uniform(0.1, 0.4)), kv_from=src)
+        if rng.random() < 0.15:
+            m["mask"] = None
+        if not share:
+            owners.append(i)
+        layers.append((m, None if rng.random() < 0.25 else int(rng.integers(20, 160))))
+    return config(layers, width=width, vocab=int(rng.integers(40, 500)), mult=float(rng.uniform(0.3, 1.2)),
+                  logit_scale=float(rng.uniform(0.1, 2.0)), emb=float(rng.uniform(0.5, 8.0)), eps=float(rng.choice([1e-5, 1e-6, 1e-4])))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [11, 12, 13, 14])
+def test_the_replay_program_on_configurations_drawn_at_random(tmp_path, seed, dtype):
+    """bin/trace_run as a user calls it, on a configuration drawn at random, under a schedule drawn at random: JSON
+    lines in, <step>.f32 files and 'done' lines out; a pool of as many tokens as live requests hold, four slots."""
+    import json
+    import os
+    import subprocess
+    import sys
+    rng = np.random.default_rng(seed)
+    cfg = random_rolesun_config(rng)
+    weights = plain.random_weights(cfg, seed, sharp=SHARP[dtype])
+    if dtype == "bfloat16":
+        weights = plain.round_to_bf16(weights)
+    folder = str(tmp_path / "model")
+    plain.write_model_folder(folder, cfg, weights, store="BF16" if dtype == "bfloat16" else "F32")
+    lengths = {f"q{i}": int(n) for i, n in enumerate(rng.choice([1, 2, 30, 77, 150, 64], size=6))}
+    ids = {r: ids_of(cfg, n, seed * 100 + i) for i, (r, n) in enumerate(lengths.items())}
+    waiting, live, at, lines, asked = list(lengths), [], {}, [], []
+    most = 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+            at[live[-1]] = 0
+        most = max(most, sum(-(-lengths[r] // 64) * 64 for r in live))
+        entries, end = [], []
+        for r in live:
+            s = int(min(lengths[r] - at[r], 1 if at[r] > 50 else rng.choice([1, 2, 3, 16, 37, 64])))
+            want = sorted(set(int(w) for w in rng.integers(0, s, size=min(s, 3))))
+            entries.append({"id": r, "tokens": ids[r][at[r]: at[r] + s], "want": want})
+            asked.append([(r, at[r] + w) for w in want])
+            at[r] += s
+            if at[r] == lengths[r]:
+                end.append(r)
+        lines.append({"step": len(lines), "entries": entries, "end": end})
+        asked[-len(entries):] = [sum(asked[-len(entries):], [])]
+        live = [r for r in live if r not in end]
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(most)],
+                       input="".join(json.dumps(l) + "\n" for l in lines), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert [l for l in p.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(len(lines))]
+    want = {r: plain.forward(cfg, weights, ids[r]) for r in ids}
+    for i, rows in enumerate(asked):
+        if rows:
+            got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+            compare(got, np.stack([want[r][t] for r, t in rows]), dtype, f"seed {seed} step {i}: {cfg['layers']}")
