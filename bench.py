@@ -443,7 +443,7 @@ def rolesun_configs(size):
     z = ROLESUN_SIZES[size]
     mixer = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "kv_rank": ROLESUN_RANK, "scale": z["dim"] ** -0.5,
              "mask": {"size": 2 * ROLESUN_CONTEXT}}
-    rolesun = {"architecture": "Rolesun", "vocab": ROLESUN_VOCAB, "width": z["width"], "residual_mult": 0.7, "logit_scale": 0.25,
+    rolesun = {"architecture": "Rolesun", "vocab": ROLESUN_VOCAB, "width": z["width"], "residual_mult": 0.5, "logit_scale": 1.0,
                "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
                "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": z["ff"]}}
                           for _ in range(z["layers"])]}
@@ -583,7 +583,7 @@ def rolesun_kernels(z, peaks):
         q_start = torch.tensor([0, t], dtype=torch.int32, device=dev)
         req, pos, slots = torch.zeros(t, dtype=torch.int32, device=dev), torch.arange(t, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
         add(f"token shift, {t} tokens", "", lambda i: ops.token_shift(x[i % c], mu, state, o1[i % c], o2[i % c], q_start, req, pos, slots), c, bytes_=t * h * 8)
-        add(f"gate + norm + residual, {t} tokens", "", lambda i: ops.gated_norm_residual(y[i % c], g[i % c], bias, one, x[i % c], o1[i % c], 0.7, 1e-6), c,
+        add(f"gate + norm + residual, {t} tokens", "", lambda i: ops.gated_norm_residual(y[i % c], g[i % c], bias, one, x[i % c], o1[i % c], 0.5, 1e-6), c,
             bytes_=t * h * 14)
         add(f"Qwen2: residual add + RMSNorm, {t} tokens", "like the two above", lambda i: ops.add_rmsnorm(x[i % c], y[i % c], gain, o1[i % c], 1e-6), c, bytes_=t * h * 12)
         width = nh * d + r + nh * d
