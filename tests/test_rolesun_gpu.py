@@ -401,3 +401,39 @@ def test_the_replay_program_on_configurations_drawn_at_random(tmp_path, seed, dt
         if rows:
             got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
             compare(got, np.stack([want[r][t] for r, t in rows]), dtype, f"seed {seed} step {i}: {cfg['layers']}")
+
+
+def test_command_line_and_sampling_options(tmp_path):
+    """python -m vllm_cpp_b200.engine.cli on a Rolesun folder, the architecture taken from config.json or named by
+    --arch: greedy ids are the plain implementation's; seeded sampling with temperature, top-k, top-p and a repetition
+    penalty gives ids of the vocabulary and the same ids when asked again."""
+    import os
+    import subprocess
+    import sys
+    cfg, page = CONFIGS["A"]
+    weights = plain.random_weights(cfg, 8, sharp=SHARP["float32"])
+    folder = str(tmp_path / "cli_model")
+    plain.write_model_folder(folder, cfg, weights, store="F32")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompt = ids_of(cfg, 21, 3)
+    base = [sys.executable, "-m", "vllm_cpp_b200.engine.cli", "--model", folder, "--dtype", "float32", "--num-gpu-blocks", "24",
+            "--max-num-seqs", "2", "--max-model-len", "128", "--max-num-batched-tokens", "64", "--ignore-eos",
+            "--prompt-ids", ",".join(map(str, prompt))]
+    env = dict(os.environ, PYTHONPATH=root)
+
+    def run(extra):
+        p = subprocess.run(base + extra, capture_output=True, text=True, timeout=600, env=env, cwd=root)
+        assert p.returncode == 0, p.stderr[-3000:]
+        return [int(t) for t in p.stdout.strip().splitlines()[-1].split(",")]
+
+    greedy = run(["--max-tokens", "6", "--temperature", "0"])
+    seq = list(prompt)
+    for tok in greedy:
+        logits = plain.forward(cfg, weights, seq)[-1]
+        assert tok == plain.greedy(logits) or (logits.max() - logits[tok]) / np.abs(logits).max() < 1e-3
+        seq.append(tok)
+    options = ["--arch", "rolesun", "--max-tokens", "12", "--temperature", "0.9", "--top-k", "20", "--top-p", "0.9",
+               "--repetition-penalty", "1.2", "--sample-seed", "5"]
+    drawn = run(options)
+    assert len(drawn) == 12 and all(0 <= t < cfg["vocab"] for t in drawn)
+    assert run(options) == drawn
