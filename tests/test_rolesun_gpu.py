@@ -306,10 +306,11 @@ def test_unequal_requests_together_on_few_pages(tmp_path, name, dtype):
     assert cache.num_free_pages() == 28
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
+@pytest.mark.parametrize("dtype,pages", [("float32", 24), ("bfloat16", 24), ("float32", 10)])
+def test_greedy_generation_through_the_entry_point(tmp_path, dtype, pages):
     """LLM.generate: the scheduler cuts the prompts under a small token budget, decode steps are captured and
-    replayed; every generated token is the plain implementation's best, or within rounding of it."""
+    replayed; every generated token is the plain implementation's best, or within rounding of it.  With 10 pages
+    requests are preempted and fed again from their first token (their state slot starts from zero again)."""
     from vllm_cpp_b200 import LLM, SamplingParams
     cfg, page = CONFIGS["A"]
     weights = plain.random_weights(cfg, 5, sharp=SHARP[dtype])
@@ -317,9 +318,12 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
         weights = plain.round_to_bf16(weights)
     folder = str(tmp_path / f"gen_{dtype}")
     plain.write_model_folder(folder, cfg, weights, store="BF16" if dtype == "bfloat16" else "F32")
-    llm = LLM(folder, dtype=dtype, block_size=page, num_gpu_blocks=24, max_num_seqs=3, max_model_len=256, max_num_batched_tokens=48)
+    llm = LLM(folder, dtype=dtype, block_size=page, num_gpu_blocks=pages, max_num_seqs=3, max_model_len=pages * page,
+              max_num_batched_tokens=48)
     prompts = [ids_of(cfg, n, 500 + n) for n in (3, 41, 100, 17)]
     outs = llm.generate(prompts, SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True))
+    if pages < 24:
+        assert llm.engine.scheduler.num_preemptions > 0
     for p, o in zip(prompts, outs):
         assert len(o) == 40
         seq = list(p)
