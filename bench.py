@@ -644,13 +644,15 @@ def rolesun_kernels(z, peaks):
         split_tiles = torch.from_numpy(part.step_arrays()[part._splits_key()](host)).to(dev)
         nsplit = host.shapes[part._splits_key()]
         need = batch * nh * nsplit
-        po, pml, tickets = torch.empty(need * r, device=dev), torch.empty(need * 2, device=dev), torch.zeros(batch, dtype=torch.int32, device=dev)
+        share = ops.decode_head_groups(nh, 1)
+        po, pml, tickets = torch.empty(need * r, device=dev), torch.empty(need * 2, device=dev), torch.zeros(batch * share, dtype=torch.int32, device=dev)
         q, o = rnd(batch, nh * r), torch.empty(batch, nh * r, dtype=bf, device=dev)
         for planes, name, like in ((1, f"attention over latent rows, decode, batch {batch}, contexts of {ROLESUN_CONTEXT}", ""),
                                    (2, f"Qwen2: attention, one kv head, decode, batch {batch}", "like the one above")):
             kv = rnd(batch * blocks + 1, planes, 1, page * r, scale=0.5)
-            add(name, like, lambda i: ops.attention_decode_mma(q, kv, o, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh, num_kv_heads=1,
-                                                               head_dim=r, page_size=page, window=0, scale=d ** -0.5, split_tiles=split_tiles, planes=planes),
+            add(name, like, lambda i: ops.attention_decode_mma(q, kv, o, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh, num_kv_heads=share,
+                                                               head_dim=r, page_size=page, window=0, scale=d ** -0.5, split_tiles=split_tiles, planes=planes,
+                                                               kv_share=share),
                 4, bytes_=batch * ROLESUN_CONTEXT * planes * r * 2)
     ops.check_status()
     return rows

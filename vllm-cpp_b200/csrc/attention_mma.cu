@@ -54,6 +54,9 @@ struct MmaAttnArgs {
                                    // and VCB_STATUS_BAD_PAGE goes to the status word
     int planes;                    // 2: a page holds keys, then values; 1: one plane of rows that are key and value
                                    // at once (attention over cached latent rows, queries already in their space)
+    int kv_share;                  // decode: this many consecutive kv heads of `nkv` are one head of the cache.  A group of more
+                                   // than 16 query heads is cut into equal groups of at most 16 that run as CTAs of their own
+                                   // instead of as passes of one CTA over the same keys (1: nkv is the cache's own count)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -317,8 +320,9 @@ attention_decode_kernel(MmaAttnArgs a) {
             PageWindow pw;
             const PageDiv pd(a.page);
             pw.init(bt, pd.div(my0 * BN), hi, a.page, lane, a.num_pages);
-            const size_t page_stride = (size_t)a.planes * a.nkv * a.page * D, head_base = (size_t)g * a.page * D,
-                         v_off = (size_t)(a.planes - 1) * a.nkv * a.page * D;
+            const int cache_heads = a.nkv / a.kv_share;
+            const size_t page_stride = (size_t)a.planes * cache_heads * a.page * D, head_base = (size_t)(g / a.kv_share) * a.page * D,
+                         v_off = (size_t)(a.planes - 1) * cache_heads * a.page * D;
             for (int tile = my0; tile < my1; ++tile, ++it) {
                 const int st = it % STAGES;
                 if (!waited && (tile + 1) * BN > pos) { pdl_wait(); waited = true; }   // the tile with this step's row
@@ -959,15 +963,15 @@ VCB_EXPORT int vcb_attention_decode_mma_planes(const void* q, const void* cache,
                                                const int* req_list, int n_list, int nsplit, float* part_o,
                                                float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
                                                int d, int page, int window, float scale, int num_pages, int* status,
-                                               int planes, void* stream) {
+                                               int planes, int kv_share, void* stream) {
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
-    if (planes != 1 && planes != 2) return VCB_ERR_BAD_ARG;
+    if ((planes != 1 && planes != 2) || kv_share < 1 || nkv % kv_share) return VCB_ERR_BAD_ARG;
     if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
-                  page, window, scale, num_pages, planes};
+                  page, window, scale, num_pages, planes, kv_share};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -980,7 +984,7 @@ VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* 
                                         void* stream) {
     return vcb_attention_decode_mma_planes(q, cache, out, q_start, ctx_lens, block_table, bt_stride, req_list, n_list, nsplit,
                                            part_o, part_ml, counters, split_tiles, nh, nkv, d, page, window, scale,
-                                           num_pages, status, 2, stream);
+                                           num_pages, status, 2, 1, stream);
 }
 
 // Prompt portions (and, in mixed batches, single tokens) on tcgen05 tensor cores: head sizes 64 and 128,
@@ -997,7 +1001,7 @@ VCB_EXPORT int vcb_attention_prefill_tc_planes(const void* q, const void* cache,
     if (planes != 1 && planes != 2) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale, num_pages, planes};
+                  window, scale, num_pages, planes, 1};
     return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 
@@ -1086,7 +1090,7 @@ VCB_EXPORT int vcb_attention_decode_mma_static(const void* q, const void* cache,
     }
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, req_list, nullptr, nsplit > 1 ? part_o : nullptr, part_ml, nsplit > 1 ? counters : nullptr,
-                  status, nullptr, bt_stride, nh, nkv, page, window, scale, num_pages, 2};
+                  status, nullptr, bt_stride, nh, nkv, page, window, scale, num_pages, 2, 1};
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
 

@@ -45,7 +45,7 @@ _SIGNATURES = {
     "vcb_sample_filtered": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "vcb_random_normal": [_P, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, _F, _F, _I, _P],
     "vcb_attention_simt_planes": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _P],
-    "vcb_attention_decode_mma_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
+    "vcb_attention_decode_mma_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _P],
     "vcb_attention_prefill_tc_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_embedding_sinusoid": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P, _I, _P],
     "vcb_token_shift": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
@@ -248,11 +248,13 @@ DECODE_MAX_SPLITS = 32
 
 def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
                          part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                         window: int, scale: float, split_tiles=None, planes: int = 2) -> None:
+                         window: int, scale: float, split_tiles=None, planes: int = 2, kv_share: int = 1) -> None:
     """Split-KV tensor-core attention for requests that bring one token each (bfloat16).  The grid has
     ``nsplit`` columns; without ``split_tiles`` every request's keys are cut into that many equal parts,
     with it (int32 [1] on the device: tiles of DECODE_KEY_TILE keys per split) a request takes as many
-    columns as its context needs, so that requests of different lengths keep all CTAs equally busy."""
+    columns as its context needs, so that requests of different lengths keep all CTAs equally busy.
+    ``kv_share`` > 1: ``num_kv_heads`` counts groups of query heads of which ``kv_share`` consecutive ones read the
+    same head of the cache (decode_head_groups): each group gets CTAs of its own."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attention_decode_mma is a bfloat16 kernel")
     _need(head_dim in MMA_HEAD_DIMS and page_size % 8 == 0,
@@ -263,6 +265,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
               and counters is not None and counters.numel() >= n_list * num_kv_heads,
               "attention_decode_mma: scratch for the split merge is too small")
     _need(planes in (1, 2), "planes must be 1 or 2")
+    _need(kv_share >= 1 and num_kv_heads % kv_share == 0, "attention_decode_mma: kv_share divides num_kv_heads")
     _check(lib().vcb_attention_decode_mma_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
@@ -272,7 +275,18 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         None if counters is None else _dev(counters, "counters", torch.int32),
         None if split_tiles is None else _dev(split_tiles, "split_tiles", torch.int32),
         num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
-        status_tensor(q.device).data_ptr(), planes, _stream()), "attention_decode_mma")
+        status_tensor(q.device).data_ptr(), planes, kv_share, _stream()), "attention_decode_mma")
+
+
+def decode_head_groups(num_heads: int, num_kv_heads: int) -> int:
+    """Into how many equal groups of at most 16 the query heads of one kv head are cut for the decode kernel
+    (its fragment has 16 rows; a larger group would walk the keys once per 16 heads in one CTA): the smallest
+    divisor of the group's size that leaves at most 16 heads, or 1 if there is none below the size itself."""
+    g = num_heads // num_kv_heads
+    for s in range(1, g):
+        if g % s == 0 and g // s <= 16:
+            return s
+    return 1
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)      # head sizes of the tcgen05 prefill attention kernel

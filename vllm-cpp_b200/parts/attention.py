@@ -105,21 +105,25 @@ class PagedAttentionKernels(Mixer):
 
     SPLIT_GRIDS = (1, 2, 3, 4, 5, 6, 8, 10, 12, 16, 20, 24, 32)
 
+    def decode_groups(self) -> int:
+        """Groups of query heads that the decode kernel runs as kv heads of their own (ops.decode_head_groups)."""
+        return self.nkv * ops.decode_head_groups(self.nh, self.nkv)
+
     def decode_slots(self, n_reqs: int) -> int:
         """Splits per kv head that a decode step may have in all: seven eighths of the places the device has
         for the kernel's CTAs (two per SM).  Filling every place was measured slower: the CTAs of the
         kernels before and after share the SMs, and a CTA that finds no place waits for a second round."""
-        return max(n_reqs, (2 * ops.sm_count() * 7 // 8) // self.nkv)
+        return max(n_reqs, (2 * ops.sm_count() * 7 // 8) // self.decode_groups())
 
     def reserve(self, n_tokens, n_reqs, device):
         if self._tensor_core_path():
             most = n_reqs * self.nh * ops.DECODE_MAX_SPLITS
             ops.scratch("attn_part_o", most * self.d, device)
             ops.scratch("attn_part_ml", most * 2, device)
-            ops.zeroed_ints("attn_tickets", n_reqs * self.nkv, device)
+            ops.zeroed_ints("attn_tickets", n_reqs * self.decode_groups(), device)
 
     def _splits_key(self):
-        return f"attn_splits_kv{self.nkv}_w{self.window}"
+        return f"attn_splits_kv{self.decode_groups()}_w{self.window}"
 
     def attend(self, q, attn, step, cache, block_table):
         if self._tensor_core_path():
@@ -134,7 +138,7 @@ class PagedAttentionKernels(Mixer):
                     longest = step.split_len or step.max_total_len
                     if self.window > 0:
                         longest = min(longest, self.window + 64)
-                    nsplit = max(1, min(-(-longest // 64), 2 * ops.sm_count() // (step.n_reqs * self.nkv),
+                    nsplit = max(1, min(-(-longest // 64), 2 * ops.sm_count() // (step.n_reqs * self.decode_groups()),
                                         ops.DECODE_MAX_SPLITS))
                     split_tiles = None
                 part_o = part_ml = counters = None
@@ -142,9 +146,11 @@ class PagedAttentionKernels(Mixer):
                     need = step.n_reqs * self.nh * nsplit
                     part_o = ops.scratch("attn_part_o", need * self.d, q.device)
                     part_ml = ops.scratch("attn_part_ml", need * 2, q.device)
-                    counters = ops.zeroed_ints("attn_tickets", step.n_reqs * self.nkv, q.device)
+                    counters = ops.zeroed_ints("attn_tickets", step.n_reqs * self.decode_groups(), q.device)
+                share = ops.decode_head_groups(self.nh, self.nkv)
                 ops.attention_decode_mma(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, None,
-                                         step.n_reqs, nsplit, part_o, part_ml, counters, split_tiles=split_tiles, **kw)
+                                         step.n_reqs, nsplit, part_o, part_ml, counters, split_tiles=split_tiles,
+                                         **dict(kw, num_kv_heads=self.nkv * share, kv_share=share))
             else:
                 tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}"]
                 ops.attention_prefill_tc(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, tiles[0], tiles[1], **kw)
