@@ -14,7 +14,7 @@
 // ------------------------------------------------- embedding with scale and sinusoidal positions
 // Entry 2i of the position vector is sin(p * f_i), entry 2i+1 is cos(p * f_i); f_i (inv_freq, float,
 // (hidden + 1) / 2 values) comes from the host.  The angle is the float product of the position and f_i;
-// sinf and cosf are the accurate ones (no fast-math build).
+// sincosf is the accurate one (no fast-math build).
 template <typename T>
 __global__ void embedding_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                           const int* __restrict__ positions, const float* __restrict__ inv_freq,
@@ -23,15 +23,17 @@ __global__ void embedding_sinusoid_kernel(const T* __restrict__ table, const int
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = (unsigned)id < (unsigned)vocab;
-    if (!ok && status && threadIdx.x == 0) atomicCAS(status, 0, VCB_STATUS_BAD_TOKEN);
+    if (!ok && status && threadIdx.x == 0 && blockIdx.y == 0) atomicCAS(status, 0, VCB_STATUS_BAD_TOKEN);
     const T* row = table + (size_t)(ok ? id : 0) * hidden;
     const float p = (float)positions[t];
     float* out = residual + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float angle = p * inv_freq[i >> 1];
-        const float pe = (i & 1) ? cosf(angle) : sinf(angle);
-        out[i] = ok ? to_f32<T>(row[i]) * scale + pe : 0.0f;
-    }
+    // one thread per pair of entries: a sine and a cosine of the same angle
+    const int pair = blockIdx.y * blockDim.x + threadIdx.x, i = 2 * pair;
+    if (i >= hidden) return;
+    float sn, cs;
+    sincosf(p * inv_freq[pair], &sn, &cs);
+    out[i] = ok ? to_f32<T>(row[i]) * scale + sn : 0.0f;
+    if (i + 1 < hidden) out[i + 1] = ok ? to_f32<T>(row[i + 1]) * scale + cs : 0.0f;
 }
 
 VCB_EXPORT int vcb_embedding_sinusoid(const void* table, const int* ids, const int* positions, const float* inv_freq,
@@ -39,13 +41,15 @@ VCB_EXPORT int vcb_embedding_sinusoid(const void* table, const int* ids, const i
                                       int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (vocab <= 0 || hidden <= 0) return VCB_ERR_BAD_ARG;
-    const int threads = hidden >= 1024 ? 256 : 128;
+    const int threads = 128, pairs = (hidden + 1) / 2;
+    dim3 grid(n_tokens, (pairs + threads - 1) / threads);
+    if (grid.y > 65535) return VCB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_F32)
-        vcb_launch(embedding_sinusoid_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, positions, inv_freq,
+        vcb_launch(embedding_sinusoid_kernel<float>, grid, threads, 0, s, (const float*)table, ids, positions, inv_freq,
                    residual, hidden, vocab, scale, status);
     else if (dtype == VCB_BF16)
-        vcb_launch(embedding_sinusoid_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids,
+        vcb_launch(embedding_sinusoid_kernel<__nv_bfloat16>, grid, threads, 0, s, (const __nv_bfloat16*)table, ids,
                    positions, inv_freq, residual, hidden, vocab, scale, status);
     else
         return VCB_ERR_BAD_ARG;
