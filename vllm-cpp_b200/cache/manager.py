@@ -26,7 +26,7 @@ from typing import Dict, List, Optional
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVSpec, PagedKVView, StateSpec, StateView
+from ..parts.base import CompositeSpec, CompositeView, PagedKVSpec, PagedKVView, StateSpec, StateView, flatten_specs
 from .block_pool import BlockPool, PageError
 
 RELEASED = -1     # table entry of a page that a window has passed
@@ -74,24 +74,7 @@ class CacheManager:
         self.state: List[StateGroup] = []
         self._where: List[Optional[tuple]] = []          # cache layer -> ("paged"|"state", group, index in group)
         for layer, spec in enumerate(cache_specs):
-            if spec is None:
-                self._where.append(None)
-            elif isinstance(spec, PagedKVSpec):
-                g = next((i for i, pg in enumerate(self.paged) if pg.spec == spec), None)
-                if g is None:
-                    self.paged.append(PagedGroup(spec, [], BlockPool(num_pages)))
-                    g = len(self.paged) - 1
-                self._where.append(("paged", g, len(self.paged[g].layers)))
-                self.paged[g].layers.append(layer)
-            elif isinstance(spec, StateSpec):
-                g = next((i for i, sg in enumerate(self.state) if sg.spec == spec), None)
-                if g is None:
-                    self.state.append(StateGroup(spec, []))
-                    g = len(self.state) - 1
-                self._where.append(("state", g, len(self.state[g].layers)))
-                self.state[g].layers.append(layer)
-            else:
-                raise TypeError(f"cache layer {layer}: unknown cache need {spec!r}")
+            self._where.append(self._register(layer, spec))
         self._free_slots: List[int] = list(range(max_num_seqs - 1, -1, -1))
         self.requests: Dict[object, RequestCache] = {}
         # every group's block tables as rows of one array (see table_rows); widened on demand
@@ -99,13 +82,36 @@ class CacheManager:
         if device is not None:
             self._allocate_device()
 
+    def _register(self, layer: int, spec):
+        """Where the cache need ``spec`` of cache layer ``layer`` lives: None, ("paged" | "state", group, index in
+        group), or ("multi", [one of these per member]) for the mixers of a CompositeSpec."""
+        if spec is None:
+            return None
+        if isinstance(spec, CompositeSpec):
+            return ("multi", [self._register(layer, part) for part in spec.parts])
+        if isinstance(spec, PagedKVSpec):
+            g = next((i for i, pg in enumerate(self.paged) if pg.spec == spec), None)
+            if g is None:
+                self.paged.append(PagedGroup(spec, [], BlockPool(self.num_pages)))
+                g = len(self.paged) - 1
+            self.paged[g].layers.append(layer)
+            return ("paged", g, len(self.paged[g].layers) - 1)
+        if isinstance(spec, StateSpec):
+            g = next((i for i, sg in enumerate(self.state) if sg.spec == spec), None)
+            if g is None:
+                self.state.append(StateGroup(spec, []))
+                g = len(self.state) - 1
+            self.state[g].layers.append(layer)
+            return ("state", g, len(self.state[g].layers) - 1)
+        raise TypeError(f"cache layer {layer}: unknown cache need {spec!r}")
+
     # ---------------------------------------------------------------- device
     @staticmethod
     def bytes_per_page(cache_specs: List[object], page_size: int, dtype: torch.dtype) -> int:
         """Device bytes that one page id costs over all paged cache layers."""
         el = torch.empty((), dtype=dtype).element_size()
         return sum(s.planes * s.num_kv_heads * page_size * s.head_dim * el
-                   for s in cache_specs if isinstance(s, PagedKVSpec))
+                   for s in flatten_specs(cache_specs) if isinstance(s, PagedKVSpec))
 
     def _allocate_device(self) -> None:
         for g in self.paged:
@@ -118,17 +124,18 @@ class CacheManager:
 
     def views(self) -> List[object]:
         """What each cache layer's mixer is handed."""
-        out = []
-        for w in self._where:
-            if w is None:
-                out.append(None)
-            elif w[0] == "paged":
-                g = self.paged[w[1]]
-                out.append(PagedKVView(g.pages[w[2]] if g.pages is not None else None, w[1], self.page_size))
-            else:
-                g = self.state[w[1]]
-                out.append(StateView(g.slots[w[2]] if g.slots is not None else None))
-        return out
+        return [self._view(w) for w in self._where]
+
+    def _view(self, w):
+        if w is None:
+            return None
+        if w[0] == "multi":
+            return CompositeView([self._view(x) for x in w[1]])
+        if w[0] == "paged":
+            g = self.paged[w[1]]
+            return PagedKVView(g.pages[w[2]] if g.pages is not None else None, w[1], self.page_size)
+        g = self.state[w[1]]
+        return StateView(g.slots[w[2]] if g.slots is not None else None)
 
     # ------------------------------------------------------------- requests
     def has_free_slot(self) -> bool:

@@ -26,21 +26,21 @@ __device__ __forceinline__ bool token_ok(int id, int vocab, int* status) {
 
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ residual, int hidden, int vocab, int* status) {
+                                 float* __restrict__ residual, int hidden, int vocab, int* status, float scale) {
     pdl_start();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = token_ok(id, vocab, status);
     const T* row = table + (size_t)(ok ? id : 0) * hidden;
     float* out = residual + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = ok ? to_f32<T>(row[i]) : 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = ok ? to_f32<T>(row[i]) * scale : 0.0f;
 }
 
 // The same for bfloat16 rows of a multiple of 8 elements: 16-byte loads, all of a thread's in flight before the
 // first is widened and stored (NV vectors a thread).
 template <int NV>
 __global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
-                                        float* __restrict__ residual, int hidden, int vocab, int* status) {
+                                        float* __restrict__ residual, int hidden, int vocab, int* status, float scale) {
     pdl_start();
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -61,14 +61,15 @@ __global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table,
         const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
         const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]),
                      d = __bfloat1622float2(p[3]);
-        out[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-        out[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+        out[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+        out[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
     }
 }
 
 // vocab: rows of the table; status (may be null): the device's status word.
-VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual, int n_tokens,
-                             int hidden, int vocab, int* status, int dtype, void* stream) {
+// scale: a constant every entry is multiplied by (a design that scales its embeddings; 1 otherwise).
+VCB_EXPORT int vcb_embedding_scaled(const void* table, const int* ids, float* residual, int n_tokens,
+                                    int hidden, int vocab, int* status, float scale, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (vocab <= 0) return VCB_ERR_BAD_ARG;
     const int threads = hidden >= 1024 ? 256 : 128;
@@ -77,18 +78,23 @@ VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual,
         const int nvec = hidden / 8;
         if (nvec <= 2 * 256)
             vcb_launch(embedding_bf16x8_kernel<2>, n_tokens, nvec <= 2 * 128 ? 128 : 256, 0, s, (const __nv_bfloat16*)table, ids, residual,
-                       hidden, vocab, status);
+                       hidden, vocab, status, scale);
         else
-            vcb_launch(embedding_bf16x8_kernel<4>, n_tokens, 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden, vocab, status);
+            vcb_launch(embedding_bf16x8_kernel<4>, n_tokens, 256, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden, vocab, status, scale);
         return vcb_last_error();
     }
     if (dtype == VCB_F32)
-        vcb_launch(embedding_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, residual, hidden, vocab, status);
+        vcb_launch(embedding_kernel<float>, n_tokens, threads, 0, s, (const float*)table, ids, residual, hidden, vocab, status, scale);
     else if (dtype == VCB_BF16)
-        vcb_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden, vocab, status);
+        vcb_launch(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)table, ids, residual, hidden, vocab, status, scale);
     else
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();
+}
+
+VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual, int n_tokens,
+                             int hidden, int vocab, int* status, int dtype, void* stream) {
+    return vcb_embedding_scaled(table, ids, residual, n_tokens, hidden, vocab, status, 1.0f, dtype, stream);
 }
 
 // ---------------------------------------------------------- add + RMSNorm

@@ -1,0 +1,277 @@
+// A feed-forward of many small experts of which every token uses a few, without the host in the loop:
+//
+//   moe_router_kernel        logits = W_r h in float, softmax over all router outputs, the `top` outputs with the
+//                            largest (score + correction) chosen, their plain scores kept as weights
+//   moe_sort_kernel          the (token, choice) pairs grouped by expert: a row for each pair in a list sorted by
+//                            expert, and the list's tiles of up to TM rows of one expert
+//   moe_expert_gemm_kernel   one product per tile against that expert's matrix; the first product gathers the
+//                            tokens' rows, computes gate and up together and applies the experts' activation
+//                              g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)
+//   moe_combine_kernel       out[t] = sum over the token's choices of weight * (the expert's row, or h[t] itself for a
+//                            router output beyond the experts: an identity expert)
+//
+// Grids are sized for the most tiles a step can have; a block beyond the step's count leaves at once, so the
+// same launches serve every routing (and a captured step).  Router, softmax, weights and all sums are float.
+// The reference has no routed feed-forward (src/layers/mlp.cpp is dense).
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------- router
+template <typename T>
+__global__ void moe_router_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr,
+                                  const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ wts,
+                                  int width, int n_out, int top) {
+    extern __shared__ float sm[];
+    float* hrow = sm;                   // [width]
+    float* score = sm + width;          // [n_out] logits, then scores
+    float* choice = score + n_out;      // [n_out] score + correction; -inf once taken
+    pdl_start();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) hrow[i] = to_f32<T>(h[(size_t)t * ldh + i]);
+    __syncthreads();
+    for (int e = warp; e < n_out; e += nwarps) {
+        const float* w = wr + (size_t)e * width;
+        float acc = 0.0f;
+        for (int i = lane; i < width; i += 32) acc = fmaf(hrow[i], w[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) score[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float m = -INFINITY;
+    for (int e = lane; e < n_out; e += 32) m = fmaxf(m, score[e]);
+    m = warp_max(m);
+    float sum = 0.0f;
+    for (int e = lane; e < n_out; e += 32) { const float p = expf(score[e] - m); score[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    for (int e = lane; e < n_out; e += 32) {
+        score[e] = score[e] / sum;
+        choice[e] = score[e] + (correction ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_out; e += 32)
+            if (choice[e] > best) { best = choice[e]; at = e; }        // the lowest index among equals of a lane
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = at;
+            wts[(size_t)t * top + k] = score[at];
+            choice[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, const float* correction, int* ids, float* wts,
+                              int n_tokens, int width, int n_out, int top, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (!h || !wr || !ids || !wts || width <= 0 || n_out <= 0 || top <= 0 || top > n_out) return VCB_ERR_BAD_ARG;
+    const size_t smem = (size_t)(width + 2 * n_out) * sizeof(float);
+    if (smem > 48 * 1024) return VCB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32) vcb_launch(moe_router_kernel<float>, n_tokens, 128, smem, s, (const float*)h, ldh, wr, correction, ids, wts, width, n_out, top);
+    else if (dtype == VCB_BF16)
+        vcb_launch(moe_router_kernel<__nv_bfloat16>, n_tokens, 128, smem, s, (const __nv_bfloat16*)h, ldh, wr, correction, ids, wts,
+                   width, n_out, top);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// --------------------------------------------------------------------------------------------- sort
+// One CTA.  ids: [pairs] router outputs; outputs >= n_experts are identity experts and get no row (pos = -1).
+// meta[0] = number of tiles.  Rows of one expert are in no particular order; every row is computed by itself.
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int pairs, int top, int n_experts, int tm,
+                                int* __restrict__ sorted_token, int* __restrict__ pos, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int* __restrict__ tile_rows, int* __restrict__ meta) {
+    extern __shared__ int smi[];
+    int* count = smi;                   // [n_experts]
+    int* cursor = smi + n_experts;      // [n_experts]
+    pdl_start();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if ((unsigned)e < (unsigned)n_experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, nt = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            cursor[e] = off;
+            for (int r0 = 0; r0 < count[e]; r0 += tm) {
+                tile_expert[nt] = e;
+                tile_row0[nt] = off + r0;
+                tile_rows[nt] = min(tm, count[e] - r0);
+                ++nt;
+            }
+            off += count[e];
+        }
+        meta[0] = nt;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if ((unsigned)e < (unsigned)n_experts) {
+            const int dst = atomicAdd(&cursor[e], 1);
+            sorted_token[dst] = p / top;
+            pos[p] = dst;
+        } else {
+            pos[p] = -1;
+        }
+    }
+}
+
+VCB_EXPORT int vcb_moe_sort(const int* ids, int pairs, int top, int n_experts, int tm, int* sorted_token, int* pos,
+                            int* tile_expert, int* tile_row0, int* tile_rows, int* meta, void* stream) {
+    if (pairs <= 0) return 0;
+    if (n_experts <= 0 || top <= 0 || tm <= 0 || (size_t)n_experts * 2 * sizeof(int) > 48 * 1024) return VCB_ERR_BAD_ARG;
+    vcb_launch(moe_sort_kernel, 1, 1024, (size_t)n_experts * 2 * sizeof(int), (cudaStream_t)stream, ids, pairs, top, n_experts,
+               tm, sorted_token, pos, tile_expert, tile_row0, tile_rows, meta);
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------------------------------ expert products
+// C[row, n] = sum_k A[src(row), k] * W_e[n, k] for the rows of one tile, W_e the tile's expert's matrix.
+// GATED: W_e = [gate rows; up rows] ([2 * N, K]), rows are gathered through sorted_token, and C (type T) receives
+// the activation of (gate, up).  Otherwise A is the sorted list itself and C is float.
+// 64 output columns per CTA, TM rows, 16-deep k slices in shared memory, float accumulation (FMA).
+#define MG_N 64
+#define MG_K 16
+
+template <typename T, int TM, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_expert_gemm_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ W, void* __restrict__ Cv, long long ldc,
+                       int N, int K, const int* __restrict__ sorted_token, const int* __restrict__ tile_expert,
+                       const int* __restrict__ tile_row0, const int* __restrict__ tile_rows, const int* __restrict__ meta,
+                       float limit, float alpha) {
+    constexpr int RM = TM / 16;          // rows per thread
+    __shared__ float As[MG_K][TM + 1];
+    __shared__ float Ws[MG_K][MG_N + 1];
+    __shared__ float Us[GATED ? MG_K : 1][MG_N + 1];
+    __shared__ int src[TM];
+    pdl_start();
+    const int tile = blockIdx.y;
+    if (tile >= meta[0]) return;
+    const int e = tile_expert[tile], r0 = tile_row0[tile], rows = tile_rows[tile];
+    const int n0 = blockIdx.x * MG_N;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int me = (int)threadIdx.x;
+    if (me < TM) src[me] = me < rows ? (GATED ? sorted_token[r0 + me] : r0 + me) : -1;
+    __syncthreads();
+    const T* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    float acc[RM][4], accu[GATED ? RM : 1][4];
+#pragma unroll
+    for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.0f; if (GATED) accu[i][j] = 0.0f; }
+
+    for (int k0 = 0; k0 < K; k0 += MG_K) {
+        for (int idx = threadIdx.x; idx < TM * MG_K; idx += 256) {
+            const int r = idx / MG_K, kk = idx % MG_K, k = k0 + kk;
+            As[kk][r] = (src[r] >= 0 && k < K) ? to_f32<T>(A[(size_t)src[r] * lda + k]) : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int idx = threadIdx.x + q * 256;
+            const int r = idx / MG_K, kk = idx % MG_K, k = k0 + kk;
+            const bool ok = n0 + r < N && k < K;
+            Ws[kk][r] = ok ? to_f32<T>(We[(size_t)(n0 + r) * K + k]) : 0.0f;
+            if (GATED) Us[kk][r] = ok ? to_f32<T>(We[(size_t)(N + n0 + r) * K + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MG_K; ++kk) {
+            float av[RM], wv[4], uv[4];
+#pragma unroll
+            for (int i = 0; i < RM; ++i) av[i] = As[kk][ty * RM + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { wv[j] = Ws[kk][tx * 4 + j]; if (GATED) uv[j] = Us[kk][tx * 4 + j]; }
+#pragma unroll
+            for (int i = 0; i < RM; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                    if (GATED) accu[i][j] = fmaf(av[i], uv[j], accu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+        const int m = ty * RM + i;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (GATED) {
+                const float g = fminf(acc[i][j], limit);
+                const float u = fminf(fmaxf(accu[i][j], -limit), limit);
+                const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+                ((T*)Cv)[(size_t)(r0 + m) * ldc + n] = from_f32<T>(y);
+            } else {
+                ((float*)Cv)[(size_t)(r0 + m) * ldc + n] = acc[i][j];
+            }
+        }
+    }
+}
+
+// gated 1: A = the tokens' rows [n, K] (T), W [E, 2 * N, K], C [pairs, N] (T).  gated 0: A [pairs, K] (T), W [E, N, K],
+// C [pairs, N] float.  max_tiles: the grid's height; tm: 16 or 64, the tile height moe_sort was given.
+VCB_EXPORT int vcb_moe_expert_gemm(const void* A, long long lda, const void* W, void* C, long long ldc, int N, int K,
+                                   const int* sorted_token, const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                                   const int* meta, int max_tiles, int tm, int gated, float limit, float alpha, int dtype,
+                                   void* stream) {
+    if (max_tiles <= 0) return 0;
+    if (!A || !W || !C || N <= 0 || K <= 0 || (tm != 16 && tm != 64) || max_tiles > 65535) return VCB_ERR_BAD_ARG;
+    dim3 grid((N + MG_N - 1) / MG_N, max_tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+#define MOE_GO(TT, TMV, G) vcb_launch(moe_expert_gemm_kernel<TT, TMV, G>, grid, 256, 0, s, (const TT*)A, lda, (const TT*)W, C, ldc, N, K, \
+                                      sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha)
+    if (dtype == VCB_F32) {
+        if (tm == 16) { if (gated) MOE_GO(float, 16, true); else MOE_GO(float, 16, false); }
+        else { if (gated) MOE_GO(float, 64, true); else MOE_GO(float, 64, false); }
+    } else if (dtype == VCB_BF16) {
+        if (tm == 16) { if (gated) MOE_GO(__nv_bfloat16, 16, true); else MOE_GO(__nv_bfloat16, 16, false); }
+        else { if (gated) MOE_GO(__nv_bfloat16, 64, true); else MOE_GO(__nv_bfloat16, 64, false); }
+    } else return VCB_ERR_BAD_ARG;
+#undef MOE_GO
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------------------------------------ combine
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ h, long long ldh, const int* __restrict__ pos,
+                                   const float* __restrict__ wts, T* __restrict__ out, int width, int top) {
+    pdl_start();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int p = pos[(size_t)t * top + k];
+            const float w = wts[(size_t)t * top + k];
+            acc += w * (p >= 0 ? y[(size_t)p * width + i] : to_f32<T>(h[(size_t)t * ldh + i]));
+        }
+        out[(size_t)t * width + i] = from_f32<T>(acc);
+    }
+}
+
+VCB_EXPORT int vcb_moe_combine(const float* y, const void* h, long long ldh, const int* pos, const float* wts, void* out,
+                               int n_tokens, int width, int top, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (!y || !h || !pos || !wts || !out || width <= 0 || top <= 0) return VCB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == VCB_F32) vcb_launch(moe_combine_kernel<float>, n_tokens, threads, 0, s, y, (const float*)h, ldh, pos, wts, (float*)out, width, top);
+    else if (dtype == VCB_BF16)
+        vcb_launch(moe_combine_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, y, (const __nv_bfloat16*)h, ldh, pos, wts,
+                   (__nv_bfloat16*)out, width, top);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}

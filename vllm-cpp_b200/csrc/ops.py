@@ -25,6 +25,7 @@ _lib = None
 _P = ctypes.c_void_p
 _I = ctypes.c_int
 _F = ctypes.c_float
+_L = ctypes.c_longlong
 
 _SIGNATURES = {
     "vcb_embedding": [_P, _P, _P, _I, _I, _I, _P],
@@ -53,6 +54,17 @@ _SIGNATURES = {
     "vcb_latent_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, ctypes.c_longlong, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_embedding_scaled": [_P, _P, _P, _I, _I, _I, _P, _F, _I, _P],
+    "vcb_norm_residual_norm": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P],
+    "vcb_decayed_state_scan": [_P, _P, _P, _P, _L, _L, _L, _L, _P, _P, _F, _F, _I, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_gated_group_norm": [_P, _L, _P, _L, _P, _I, _P, _L, _I, _I, _I, _I, _F, _I, _P],
+    "vcb_scaled_sum": [_P, _P, _P, _L, _F, _F, _I, _P],
+    "vcb_qk_norm_cache_write": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
+    "vcb_attention_biased": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _I, _P],
+    "vcb_moe_router": [_P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_moe_sort": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "vcb_moe_expert_gemm": [_P, _L, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _I, _P],
+    "vcb_moe_combine": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
 }
 
 
@@ -151,15 +163,16 @@ def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
 
 
 # --------------------------------------------------------------------- ops
-def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[t] = float(table[ids[t]]); ids int32 [n], residual float32 [n, hidden].  An id outside the
+def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor, scale: float = 1.0) -> None:
+    """residual[t] = float(table[ids[t]]) * scale; ids int32 [n], residual float32 [n, hidden].  An id outside the
     table leaves a row of zeros and code 12 in the status word."""
     n, hidden = residual.shape
     _need(table.dim() == 2 and table.shape[1] == hidden, "embedding table width differs from the residual's")
     _need(ids.numel() == n, "one id per residual row")
-    _check(lib().vcb_embedding(_dev(table, "table"), _dev(ids, "ids", torch.int32),
-                               _dev(residual, "residual", torch.float32), n, hidden, table.shape[0],
-                               status_tensor(table.device).data_ptr(), dtype_code(table.dtype), _stream()), "embedding")
+    _check(lib().vcb_embedding_scaled(_dev(table, "table"), _dev(ids, "ids", torch.int32),
+                                      _dev(residual, "residual", torch.float32), n, hidden, table.shape[0],
+                                      status_tensor(table.device).data_ptr(), float(scale), dtype_code(table.dtype),
+                                      _stream()), "embedding")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
@@ -808,6 +821,210 @@ def gated_norm_residual(y: torch.Tensor, gate: Optional[torch.Tensor], gate_bias
                                          _dev(x, "x", torch.float32), None if plain is None else _dev(plain, "plain"),
                                          n, hidden, float(mult), float(eps), dtype_code(y.dtype), _stream()),
            "gated_norm_residual")
+
+
+def norm_residual_norm(y: torch.Tensor, gain: torch.Tensor, x: torch.Tensor, eps: float,
+                       next_gain: Optional[torch.Tensor] = None, next_out: Optional[torch.Tensor] = None,
+                       next_eps: float = 0.0) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * gain in float32 in place (``gain``: whatever multiplies the normed result per
+    coordinate); with ``next_out``: next_out = x / sqrt(mean(x^2) + next_eps) * next_gain in the activations' type, the
+    input of the sublayer that follows."""
+    n, hidden = x.shape
+    _need(y.shape == x.shape and gain.numel() == hidden, "norm_residual_norm: shapes")
+    if next_out is not None:
+        _need(next_gain is not None and next_gain.numel() == hidden and next_out.shape == x.shape and next_out.dtype == y.dtype,
+              "norm_residual_norm: the next norm's gain and output")
+    _check(lib().vcb_norm_residual_norm(_dev(y, "y"), _dev(gain, "gain", torch.float32), _dev(x, "x", torch.float32),
+                                        None if next_out is None else _dev(next_gain, "next_gain", torch.float32),
+                                        None if next_out is None else _dev(next_out, "next_out"), n, hidden, float(eps),
+                                        float(next_eps), dtype_code(y.dtype), _stream()), "norm_residual_norm")
+
+
+# ------------------------------------------------- mixers with a decaying matrix state
+def _rows(t: torch.Tensor, name: str, dtype) -> None:
+    _need(t.is_cuda and t.dim() == 2 and t.stride(1) == 1 and t.dtype == dtype, f"{name}: rows with unit inner stride of {dtype} on the GPU")
+
+
+def decayed_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                       q_start: torch.Tensor, state_slots: torch.Tensor, n_reqs: int, *, num_heads: int,
+                       decay_pre: Optional[torch.Tensor] = None, decay_bias: Optional[torch.Tensor] = None,
+                       decay_const: Optional[torch.Tensor] = None, tau: float = 1.0, q_scale: float = 1.0,
+                       silu_inputs: bool = False) -> None:
+    """Per request and head, over the step's tokens:  S = diag(a_t) S + k_t v_t^T;  out_t = S^T q_t, with S (float32
+    [dk, dv]) read from and left in the request's slot of ``state`` [slots, heads, dk, dv].  q, k [n, heads * dk] and
+    v [n, heads * dv] are rows (strided views allowed) of the activations' type; out float32 [n, heads * dv].  The decay:
+    ``decay_pre`` ([n, heads * dk]) gives a_t = sigmoid(decay_pre + decay_bias)^(1 / tau) per key channel;
+    ``decay_const`` (float32 [heads]) one number per head; neither: 1.  ``silu_inputs``: q, k and v pass through
+    silu; ``q_scale`` multiplies q."""
+    n = q.shape[0]
+    H = num_heads
+    _need(q.shape[1] % H == 0 and v.shape[1] % H == 0, "decayed_state_scan: widths must be multiples of the head count")
+    dk, dv = q.shape[1] // H, v.shape[1] // H
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _rows(t, name, q.dtype)
+    _need(k.shape == q.shape and v.shape[0] == n, "decayed_state_scan: q, k and v of one step")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv),
+          "decayed_state_scan: state float32 [slots, heads, dk, dv]")
+    _rows(out, "out", torch.float32)
+    _need(out.shape == (n, H * dv), "decayed_state_scan: out [n, heads * dv]")
+    if decay_pre is not None:
+        _rows(decay_pre, "decay_pre", q.dtype)
+        _need(decay_pre.shape == q.shape and decay_const is None and tau > 0, "decayed_state_scan: one decay per key channel")
+        _need(decay_bias is None or decay_bias.numel() == H * dk, "decayed_state_scan: decay_bias [heads * dk]")
+    if decay_const is not None:
+        _need(decay_const.numel() == H, "decayed_state_scan: decay_const [heads]")
+    _check(lib().vcb_decayed_state_scan(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), None if decay_pre is None else decay_pre.data_ptr(),
+        q.stride(0), k.stride(0), v.stride(0), 0 if decay_pre is None else decay_pre.stride(0),
+        None if decay_bias is None else _dev(decay_bias, "decay_bias", torch.float32),
+        None if decay_const is None else _dev(decay_const, "decay_const", torch.float32),
+        1.0 / float(tau), float(q_scale), 1 if silu_inputs else 0, state.data_ptr(), out.data_ptr(), out.stride(0),
+        _dev(q_start, "q_start", torch.int32), _dev(state_slots, "state_slots", torch.int32), n_reqs, H, dk, dv,
+        dtype_code(q.dtype), _stream()), "decayed_state_scan")
+
+
+def gated_group_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor, *, group: int,
+                     eps: float, gate_act: str = "sigmoid") -> None:
+    """out = o / sqrt(mean over each group of ``group`` channels of o^2 + eps) * weight[channel % len(weight)] * act(gate);
+    o float32 [n, C], gate and out rows of the activations' type, act "sigmoid" or "silu"."""
+    n, C = o.shape
+    _rows(o, "o", torch.float32)
+    _rows(out, "out", out.dtype)
+    _need(out.shape == o.shape and (C % group == 0) and weight.numel() in (group, C), "gated_group_norm: shapes")
+    _need(gate_act in ("sigmoid", "silu"), "gated_group_norm: gate_act is 'sigmoid' or 'silu'")
+    if gate is not None:
+        _rows(gate, "gate", out.dtype)
+        _need(gate.shape == o.shape, "gated_group_norm: gate like o")
+    _check(lib().vcb_gated_group_norm(o.data_ptr(), o.stride(0), None if gate is None else gate.data_ptr(),
+                                      0 if gate is None else gate.stride(0), _dev(weight, "weight", torch.float32),
+                                      weight.numel(), out.data_ptr(), out.stride(0), n, C, group,
+                                      1 if gate_act == "silu" else 0, float(eps), dtype_code(out.dtype), _stream()),
+           "gated_group_norm")
+
+
+def scaled_sum(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor, a: float, b: float) -> None:
+    """out = a * x + b * y, computed in float and rounded once."""
+    _need(x.shape == y.shape == out.shape and x.dtype == y.dtype == out.dtype, "scaled_sum: one shape, one type")
+    _check(lib().vcb_scaled_sum(_dev(x, "x"), _dev(y, "y"), _dev(out, "out"), x.numel(), float(a), float(b),
+                                dtype_code(x.dtype), _stream()), "scaled_sum")
+
+
+# ------------------------------------------------- attention with capped scores and a bias by distance
+def qk_norm_cache_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, wq: Optional[torch.Tensor],
+                        wk: Optional[torch.Tensor], q_out: torch.Tensor, cache: torch.Tensor, positions, req_of_token,
+                        block_table, *, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, row: int,
+                        page_size: int, eps: float, write_kv: bool) -> None:
+    """A token's row of ``proj`` holds its query projection at ``q_off`` (heads * head_dim), key projection at ``k_off``
+    (kv heads * head_dim) and values at ``v_off`` (kv heads * v_head_dim).  Queries and keys are RMS-normed over the whole
+    projection with the gains ``wq`` / ``wk`` (None: left as they are); queries go to ``q_out``, keys and values into
+    the token's slot of the cache, whose rows are ``row`` elements wide."""
+    n = proj.shape[0]
+    _rows(proj, "proj", proj.dtype)
+    _need(q_out.shape == (n, num_heads * head_dim) and q_out.dtype == proj.dtype and cache.dtype == proj.dtype, "qk_norm_cache_write: types")
+    _need(wq is None or wq.numel() == num_heads * head_dim, "qk_norm_cache_write: one query gain per channel")
+    _need(wk is None or wk.numel() == num_kv_heads * head_dim, "qk_norm_cache_write: one key gain per channel")
+    _need(cache.is_contiguous() and cache.numel() == cache.shape[0] * 2 * num_kv_heads * page_size * row,
+          "qk_norm_cache_write: a cache of key and value planes with rows of `row` elements")
+    _check(lib().vcb_qk_norm_cache_write(
+        proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, None if wq is None else _dev(wq, "wq", torch.float32),
+        None if wk is None else _dev(wk, "wk", torch.float32), _dev(q_out, "q_out"), cache.data_ptr(),
+        _dev(positions, "positions", torch.int32), _dev(req_of_token, "req_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], n, num_heads, num_kv_heads, head_dim,
+        v_head_dim, row, page_size, cache.shape[0], 1 if write_kv else 0, float(eps), status_tensor(proj.device).data_ptr(),
+        dtype_code(proj.dtype), _stream()), "qk_norm_cache_write")
+
+
+def attention_biased(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], positions,
+                     req_of_token, block_table, bias: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int,
+                     head_dim: int, v_head_dim: int, row: int, page_size: int, window: int, scale: float, cap: float) -> None:
+    """Paged attention with  score = cap * tanh(scale * q.k / cap) + bias[min(distance, len(bias) - 1), head]  (cap <= 0: no
+    cap; bias float32 [distances, heads] or None), softmax over the keys the window leaves, values of ``v_head_dim``,
+    and out *= sigmoid(gate) when a gate ([n, heads * v_head_dim] rows) is given."""
+    n = q.shape[0]
+    _need(q.shape == (n, num_heads * head_dim) and out.shape == (n, num_heads * v_head_dim) and out.dtype == q.dtype
+          and cache.dtype == q.dtype, "attention_biased: shapes or types")
+    _need(v_head_dim <= 256 and head_dim <= 1024, "attention_biased: head sizes up to 1024 (keys) and 256 (values)")
+    if gate is not None:
+        _rows(gate, "gate", q.dtype)
+        _need(gate.shape == out.shape, "attention_biased: gate like out")
+    if bias is not None:
+        _need(bias.dim() == 2 and bias.shape[1] == num_heads, "attention_biased: bias [distances, heads]")
+    _check(lib().vcb_attention_biased(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), None if gate is None else gate.data_ptr(),
+        0 if gate is None else gate.stride(0), _dev(positions, "positions", torch.int32),
+        _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        None if bias is None else _dev(bias, "bias", torch.float32), 0 if bias is None else bias.shape[0], n, num_heads,
+        num_kv_heads, head_dim, v_head_dim, row, page_size, window, float(scale), float(cap), cache.shape[0],
+        status_tensor(q.device).data_ptr(), dtype_code(q.dtype), _stream()), "attention_biased")
+
+
+# ------------------------------------------------- routed experts
+MOE_TILE_ROWS = (16, 64)       # heights of the expert products' tiles: short for steps of few tokens
+
+
+def moe_tile_rows(n_tokens: int, top: int, n_experts: int) -> int:
+    """The tile height for a step: 64 rows once an expert gets that many tokens on average, else 16."""
+    return 64 if n_tokens * top >= 64 * n_experts else 16
+
+
+def moe_max_tiles(n_tokens: int, top: int, n_experts: int, tm: int) -> int:
+    """The most tiles a step can have: every expert may end with a tile that is not full."""
+    pairs = n_tokens * top
+    return min(pairs, pairs // tm + n_experts)
+
+
+def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
+               weights: torch.Tensor) -> None:
+    """For every row of h: scores = softmax(w_router h) in float32 over all router outputs; ids [n, top] = the outputs
+    with the largest score + correction (the lower index wins among equals), weights [n, top] = their plain scores."""
+    n, width = h.shape
+    _rows(h, "h", h.dtype)
+    top = ids.shape[1]
+    _need(w_router.shape[1] == width and ids.shape == (n, top) and weights.shape == (n, top), "moe_router: shapes")
+    _need(correction is None or correction.numel() == w_router.shape[0], "moe_router: one correction per router output")
+    _check(lib().vcb_moe_router(h.data_ptr(), h.stride(0), _dev(w_router, "w_router", torch.float32),
+                                None if correction is None else _dev(correction, "correction", torch.float32),
+                                _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), n, width,
+                                w_router.shape[0], top, dtype_code(h.dtype), _stream()), "moe_router")
+
+
+def moe_sort(ids: torch.Tensor, n_experts: int, tm: int, sorted_token, pos, tile_expert, tile_row0, tile_rows, meta) -> None:
+    """Groups the (token, choice) pairs of ``ids`` [n, top] by expert (see moe.cu); outputs >= n_experts get pos -1."""
+    n, top = ids.shape
+    for t, name in ((sorted_token, "sorted_token"), (pos, "pos"), (tile_expert, "tile_expert"), (tile_row0, "tile_row0"),
+                    (tile_rows, "tile_rows"), (meta, "meta")):
+        _dev(t, name, torch.int32)
+    _need(sorted_token.numel() >= n * top and pos.numel() >= n * top, "moe_sort: a row per pair")
+    _need(tile_expert.numel() >= moe_max_tiles(n, top, n_experts, tm), "moe_sort: room for every tile")
+    _check(lib().vcb_moe_sort(_dev(ids, "ids", torch.int32), n * top, top, n_experts, tm, sorted_token.data_ptr(), pos.data_ptr(),
+                              tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr(), meta.data_ptr(), _stream()),
+           "moe_sort")
+
+
+def moe_expert_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sorted_token, tile_expert, tile_row0, tile_rows, meta,
+                    max_tiles: int, tm: int, *, gated: bool, limit: float = 0.0, alpha: float = 0.0) -> None:
+    """The experts' products over the tiles of moe_sort.  gated: a [n, K] the tokens' rows, w [E, 2 * N, K] gate rows then
+    up rows, out [pairs, N] of the activations' type = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit),
+    u = clamp(up, -limit, limit).  Not gated: a [pairs, K] the sorted rows, w [E, N, K], out [pairs, N] float32."""
+    _rows(a, "a", a.dtype)
+    _need(w.dim() == 3 and w.is_contiguous() and w.dtype == a.dtype and w.shape[2] == a.shape[1], "moe_expert_gemm: w [E, N, K]")
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    _rows(out, "out", a.dtype if gated else torch.float32)
+    _need(out.shape[1] == N and tm in MOE_TILE_ROWS, "moe_expert_gemm: out [pairs, N]")
+    _check(lib().vcb_moe_expert_gemm(a.data_ptr(), a.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), N, a.shape[1],
+                                     sorted_token.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr(),
+                                     meta.data_ptr(), max_tiles, tm, 1 if gated else 0, float(limit), float(alpha),
+                                     dtype_code(a.dtype), _stream()), "moe_expert_gemm")
+
+
+def moe_combine(y: torch.Tensor, h: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_k weights[t, k] * (y[pos[t, k]] if pos[t, k] >= 0 else h[t]); y float32 [pairs, width]."""
+    n, width = out.shape
+    _rows(h, "h", out.dtype)
+    _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[1] == width and h.shape == out.shape, "moe_combine: shapes")
+    _check(lib().vcb_moe_combine(y.data_ptr(), h.data_ptr(), h.stride(0), _dev(pos, "pos", torch.int32),
+                                 _dev(weights, "weights", torch.float32), _dev(out, "out"), n, width, weights.shape[1],
+                                 dtype_code(out.dtype), _stream()), "moe_combine")
 
 
 # ------------------------------------------------------------------ latent attention

@@ -1,0 +1,248 @@
+// Mixers whose memory is a matrix per head that decays and takes up an outer product at every token:
+//
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T        S: [dk, dv] float, one per (request, head), zero at admission
+//     o_t = S_t^T q_t
+//
+//   decayed_state_scan_kernel   runs the recurrence over a step's tokens, request by request, from the state the
+//                               request's slot holds, and leaves the new state there.  The decay a_t is either one
+//                               number per head (constant over tokens and key channels) or one per key channel and
+//                               token, sigmoid(z + b)^(1/tau) of a projection z, computed here through its logarithm.
+//                               q, k and v may pass through silu on the way in, q through a constant factor.
+//   gated_group_norm_kernel     RMS norm of the result over groups of channels (a head, or all heads together)
+//                               times silu or sigmoid of a gate, rounded to the activations' type for the output product.
+//
+// The state, the decays and their logarithms, the activations, the sums and the norm are float whatever the
+// storage type T of the projections is.  The reference has no recurrent mixer (its one mixer is
+// src/layers/attention.cpp).
+#include "common.cuh"
+
+struct ScanArgs {
+    const void* q;              // [n, H * dk] rows of the step's tokens, row stride ldq (elements)
+    const void* k;
+    const void* v;              // [n, H * dv]
+    const void* decay_pre;      // [n, H * dk] or null: pre-activation of the per-channel decay
+    long long ldq, ldk, ldv, ldd;
+    const float* decay_bias;    // [H * dk] or null
+    const float* decay_const;   // [H] or null: the decay of a head when decay_pre is null (1 if both are null)
+    float inv_tau, q_scale;
+    int act;                    // 1: silu on q, k and v
+    float* state;               // [slots][H][dk][dv]
+    float* out;                 // [n, H * dv], row stride ldo
+    long long ldo;
+    const int* q_start;
+    const int* state_slots;
+    int H, dk, dv, chunk;       // chunk: tokens staged in shared memory at a time
+};
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+// ln(sigmoid(z)) without cancellation on either side
+__device__ __forceinline__ float log_sigmoid_f(float z) { return z < 0.0f ? z - log1pf(expf(z)) : -log1pf(expf(-z)); }
+
+// Grid (request, head, tile of value channels); block (DVT value channels, parts): thread (x, y) keeps rows
+// y * DKP .. y * DKP + DKP - 1 of column x of S in registers.  Key channels beyond dk are padded with k = q = 0.
+template <typename T, int DKP>
+__global__ void decayed_state_scan_kernel(ScanArgs a) {
+    extern __shared__ float sm[];
+    pdl_start();
+    const int r = blockIdx.x, h = blockIdx.y, dvt = blockDim.x, col0 = blockIdx.z * dvt;
+    const int tx = threadIdx.x, part = threadIdx.y, parts = blockDim.y;
+    const int dkpad = parts * DKP, TC = a.chunk;
+    float* qs = sm;
+    float* ks = qs + TC * dkpad;
+    float* as = ks + TC * dkpad;
+    float* vs = as + TC * dkpad;
+    float* ps = vs + TC * dvt;
+    const int row0 = a.q_start[r], row1 = a.q_start[r + 1];
+    const int col = col0 + tx;
+    const bool col_ok = col < a.dv;
+    float* st = a.state + (((size_t)a.state_slots[r] * a.H + h) * a.dk) * a.dv;
+    float S[DKP];
+#pragma unroll
+    for (int i = 0; i < DKP; ++i) {
+        const int kr = part * DKP + i;
+        S[i] = (col_ok && kr < a.dk) ? st[(size_t)kr * a.dv + col] : 0.0f;
+    }
+    const int tid = part * dvt + tx, nthreads = dvt * parts;
+    const float dconst = a.decay_const ? a.decay_const[h] : 1.0f;
+    const T* q = (const T*)a.q;
+    const T* k = (const T*)a.k;
+    const T* v = (const T*)a.v;
+    const T* dp = (const T*)a.decay_pre;
+    for (int c0 = row0; c0 < row1; c0 += TC) {
+        const int tc = min(TC, row1 - c0);
+        __syncthreads();                          // the chunk before has been read
+        for (int idx = tid; idx < tc * dkpad; idx += nthreads) {
+            const int tt = idx / dkpad, i = idx - tt * dkpad;
+            float qv = 0.0f, kv = 0.0f, av = 1.0f;
+            if (i < a.dk) {
+                const size_t row = (size_t)(c0 + tt);
+                const int c = h * a.dk + i;
+                qv = to_f32<T>(q[row * a.ldq + c]);
+                kv = to_f32<T>(k[row * a.ldk + c]);
+                if (a.act) { qv = silu_f(qv); kv = silu_f(kv); }
+                qv *= a.q_scale;
+                if (dp) {
+                    const float z = to_f32<T>(dp[row * a.ldd + c]) + (a.decay_bias ? a.decay_bias[c] : 0.0f);
+                    av = expf(log_sigmoid_f(z) * a.inv_tau);
+                } else {
+                    av = dconst;
+                }
+            }
+            qs[idx] = qv;
+            ks[idx] = kv;
+            as[idx] = av;
+        }
+        for (int idx = tid; idx < tc * dvt; idx += nthreads) {
+            const int tt = idx / dvt, j = idx - tt * dvt, c = col0 + j;
+            float vv = c < a.dv ? to_f32<T>(v[(size_t)(c0 + tt) * a.ldv + h * a.dv + c]) : 0.0f;
+            if (a.act) vv = silu_f(vv);
+            vs[idx] = vv;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < tc; ++tt) {
+            const float vv = vs[tt * dvt + tx];
+            const float* qq = qs + tt * dkpad + part * DKP;
+            const float* kk = ks + tt * dkpad + part * DKP;
+            const float* aa = as + tt * dkpad + part * DKP;
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DKP; ++i) {
+                S[i] = fmaf(aa[i], S[i], kk[i] * vv);
+                acc = fmaf(S[i], qq[i], acc);
+            }
+            ps[(part * TC + tt) * dvt + tx] = acc;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < tc * dvt; idx += nthreads) {
+            const int tt = idx / dvt, j = idx - tt * dvt, c = col0 + j;
+            if (c >= a.dv) continue;
+            float s = 0.0f;
+            for (int p = 0; p < parts; ++p) s += ps[(p * TC + tt) * dvt + j];
+            a.out[(size_t)(c0 + tt) * a.ldo + h * a.dv + c] = s;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DKP; ++i) {
+        const int kr = part * DKP + i;
+        if (col_ok && kr < a.dk) st[(size_t)kr * a.dv + col] = S[i];
+    }
+}
+
+template <typename T>
+static int launch_scan(const ScanArgs& a, int n_reqs, cudaStream_t s) {
+    // rows of S a thread keeps: few for small heads, so that the threads of a block stay many
+    const int dkp = a.dk <= 64 ? 16 : a.dk <= 256 ? 32 : 64;
+    const int parts = (a.dk + dkp - 1) / dkp;
+    if (parts > 8) return VCB_ERR_UNSUPPORTED;
+    // a narrow tile of value channels when the grid would otherwise leave most SMs without a block
+    const long long wide_blocks = (long long)n_reqs * a.H * ((a.dv + 63) / 64);
+    const int dvt = (a.dv <= 32 || wide_blocks < 2LL * vcb_sm_count()) ? 32 : 64;
+    const int dkpad = parts * dkp;
+    int chunk = 16;
+    auto bytes = [&](int tc) { return (size_t)tc * (3 * dkpad + dvt + parts * dvt) * sizeof(float); };
+    while (chunk > 1 && bytes(chunk) > 48 * 1024) chunk >>= 1;
+    ScanArgs b = a;
+    b.chunk = chunk;
+    dim3 grid(n_reqs, a.H, (a.dv + dvt - 1) / dvt), block(dvt, parts);
+    if (dkp == 16) vcb_launch(decayed_state_scan_kernel<T, 16>, grid, block, bytes(chunk), s, b);
+    else if (dkp == 32) vcb_launch(decayed_state_scan_kernel<T, 32>, grid, block, bytes(chunk), s, b);
+    else vcb_launch(decayed_state_scan_kernel<T, 64>, grid, block, bytes(chunk), s, b);
+    return vcb_last_error();
+}
+
+VCB_EXPORT int vcb_decayed_state_scan(const void* q, const void* k, const void* v, const void* decay_pre,
+                                      long long ldq, long long ldk, long long ldv, long long ldd,
+                                      const float* decay_bias, const float* decay_const, float inv_tau, float q_scale,
+                                      int act, float* state, float* out, long long ldo, const int* q_start,
+                                      const int* state_slots, int n_reqs, int H, int dk, int dv, int dtype, void* stream) {
+    if (n_reqs <= 0) return 0;
+    if (!q || !k || !v || !state || !out || H <= 0 || dk <= 0 || dv <= 0 || H > 65535) return VCB_ERR_BAD_ARG;
+    if ((dv + 31) / 32 > 65535) return VCB_ERR_UNSUPPORTED;
+    ScanArgs a{q, k, v, decay_pre, ldq, ldk, ldv, ldd, decay_bias, decay_const, inv_tau, q_scale, act, state, out, ldo,
+               q_start, state_slots, H, dk, dv, 0};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32) return launch_scan<float>(a, n_reqs, s);
+    if (dtype == VCB_BF16) return launch_scan<__nv_bfloat16>(a, n_reqs, s);
+    return VCB_ERR_BAD_ARG;
+}
+
+// ------------------------------------------------------------- norm over groups of channels, times a gate
+// One CTA per token.  o: float [n, C]; groups of `group` consecutive channels are normed apart,
+// out = o / sqrt(mean_group(o^2) + eps) * w[channel % wlen] * act(gate), act 0: sigmoid, 1: silu.
+// One group (group == C): the CTA reduces together; several: a warp per group.
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ o, long long ldo, const T* __restrict__ gate, long long ldg,
+                                        const float* __restrict__ w, int wlen, T* __restrict__ out, long long ldout,
+                                        int C, int group, int act, float eps) {
+    __shared__ float scratch[33];
+    pdl_start();
+    const float* orow = o + (size_t)blockIdx.x * ldo;
+    const T* grow = gate ? gate + (size_t)blockIdx.x * ldg : nullptr;
+    T* dst = out + (size_t)blockIdx.x * ldout;
+    if (group >= C) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < C; i += blockDim.x) ss += orow[i] * orow[i];
+        ss = block_sum(ss, scratch);
+        const float r = 1.0f / sqrtf(ss / (float)C + eps);
+        for (int i = threadIdx.x; i < C; i += blockDim.x) {
+            float y = orow[i] * r * w[i % wlen];
+            if (grow) { const float g = to_f32<T>(grow[i]); y *= act ? silu_f(g) : sigmoid_f(g); }
+            dst[i] = from_f32<T>(y);
+        }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int g0 = warp * group; g0 < C; g0 += nwarps * group) {
+        const int len = min(group, C - g0);
+        float ss = 0.0f;
+        for (int i = lane; i < len; i += 32) ss += orow[g0 + i] * orow[g0 + i];
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)len + eps);
+        for (int i = lane; i < len; i += 32) {
+            float y = orow[g0 + i] * r * w[(g0 + i) % wlen];
+            if (grow) { const float g = to_f32<T>(grow[g0 + i]); y *= act ? silu_f(g) : sigmoid_f(g); }
+            dst[g0 + i] = from_f32<T>(y);
+        }
+    }
+}
+
+VCB_EXPORT int vcb_gated_group_norm(const float* o, long long ldo, const void* gate, long long ldg, const float* w, int wlen,
+                                    void* out, long long ldout, int n_tokens, int C, int group, int act, float eps,
+                                    int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (!o || !w || !out || C <= 0 || group <= 0 || wlen <= 0) return VCB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = C >= 2048 ? 512 : C >= 512 ? 256 : 128;
+    if (dtype == VCB_F32)
+        vcb_launch(gated_group_norm_kernel<float>, n_tokens, threads, 0, s, o, ldo, (const float*)gate, ldg, w, wlen, (float*)out,
+                   ldout, C, group, act, eps);
+    else if (dtype == VCB_BF16)
+        vcb_launch(gated_group_norm_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, o, ldo, (const __nv_bfloat16*)gate, ldg, w, wlen,
+                   (__nv_bfloat16*)out, ldout, C, group, act, eps);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------- two mixers side by side
+// out = a * x + b * y, in float, rounded once.
+template <typename T>
+__global__ void scaled_sum_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ out, long long n, float a, float b) {
+    pdl_start();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(a * to_f32<T>(x[i]) + b * to_f32<T>(y[i]));
+}
+
+VCB_EXPORT int vcb_scaled_sum(const void* x, const void* y, void* out, long long n, float a, float b, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    const long long want = (n + 255) / 256, cap = (long long)vcb_sm_count() * 16;
+    const int blocks = (int)(want < cap ? want : cap);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32) vcb_launch(scaled_sum_kernel<float>, blocks, 256, 0, s, (const float*)x, (const float*)y, (float*)out, n, a, b);
+    else if (dtype == VCB_BF16)
+        vcb_launch(scaled_sum_kernel<__nv_bfloat16>, blocks, 256, 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y,
+                   (__nv_bfloat16*)out, n, a, b);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}

@@ -297,3 +297,75 @@ VCB_EXPORT int vcb_gated_norm_residual(const void* y, const void* a, const float
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();
 }
+
+// ------------------------------------- norm on a result, residual addition, and the norm before the next sublayer
+// One CTA per row:  x += (y / sqrt(mean(y^2) + eps)) * gain;  next = (x / sqrt(mean(x^2) + eps_next)) * next_gain
+// (next may be null: then only the addition).  gain holds whatever multiplies the normed result coordinate by
+// coordinate (a norm's gain times a layer scale).  The new row stays in registers between the two reductions
+// when it fits (up to PER values a thread), else x is read again.
+template <typename T, int PER>
+__global__ void norm_residual_norm_kernel(const T* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x,
+                                          const float* __restrict__ next_gain, T* __restrict__ next, int hidden,
+                                          float eps, float eps_next) {
+    __shared__ float scratch[33];
+    pdl_start();
+    const size_t row = (size_t)blockIdx.x * hidden;
+    const bool kept = hidden <= PER * (int)blockDim.x;
+    float v[PER];
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float z = to_f32<T>(y[row + i]);
+        ss += z * z;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+    float sx = 0.0f;
+#pragma unroll
+    for (int c = 0; c < PER; ++c) v[c] = 0.0f;
+    if (kept) {
+#pragma unroll
+        for (int c = 0; c < PER; ++c) {
+            const int i = threadIdx.x + c * blockDim.x;
+            if (i < hidden) {
+                v[c] = x[row + i] + (to_f32<T>(y[row + i]) * r) * gain[i];
+                x[row + i] = v[c];
+                sx += v[c] * v[c];
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float nv = x[row + i] + (to_f32<T>(y[row + i]) * r) * gain[i];
+            x[row + i] = nv;
+            sx += nv * nv;
+        }
+    }
+    if (!next) return;
+    sx = block_sum(sx, scratch);
+    const float rn = 1.0f / sqrtf(sx / (float)hidden + eps_next);
+    if (kept) {
+#pragma unroll
+        for (int c = 0; c < PER; ++c) {
+            const int i = threadIdx.x + c * blockDim.x;
+            if (i < hidden) next[row + i] = from_f32<T>(v[c] * rn * next_gain[i]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) next[row + i] = from_f32<T>(x[row + i] * rn * next_gain[i]);
+    }
+}
+
+VCB_EXPORT int vcb_norm_residual_norm(const void* y, const float* gain, float* x, const float* next_gain, void* next,
+                                      int n_tokens, int hidden, float eps, float eps_next, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (hidden <= 0 || !y || !gain || !x || (next && !next_gain)) return VCB_ERR_BAD_ARG;
+    const int threads = hidden >= 4096 ? 512 : hidden >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        vcb_launch(norm_residual_norm_kernel<float, 16>, n_tokens, threads, 0, s, (const float*)y, gain, x, next_gain, (float*)next,
+                   hidden, eps, eps_next);
+    else if (dtype == VCB_BF16)
+        vcb_launch(norm_residual_norm_kernel<__nv_bfloat16, 16>, n_tokens, threads, 0, s, (const __nv_bfloat16*)y, gain, x, next_gain,
+                   (__nv_bfloat16*)next, hidden, eps, eps_next);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}

@@ -21,7 +21,7 @@ import torch
 
 from ..cache.manager import CacheManager, cdiv
 from ..config.engine_config import ConfigError, EngineConfig
-from ..parts.base import StateSpec
+from ..parts.base import StateSpec, flatten_specs
 
 LIBRARY_RESERVE = 384 << 20       # cuBLAS and cuBLASLt workspaces, graph pools, growth of the CUDA context
 SAMPLER_SLOTS = 2                 # sampling.sampler.Sampler.SLOTS
@@ -103,12 +103,13 @@ def plan(cfg: EngineConfig, total: int, in_place: int, slices: List[Tuple[str, i
 def plan_for_model(cfg: EngineConfig, model, total: int, in_place: int, max_model_len: int, sm_count: int) -> MemoryPlan:
     """``plan`` with the slices of ``model`` (a parts.model.DecoderModel whose weights are loaded)."""
     specs = model.cache_specs()
+    simple = flatten_specs(specs)
     el = torch.empty((), dtype=model.dtype).element_size()
     workspace = model.workspace_bytes(cfg.max_num_batched_tokens, cfg.max_num_seqs, cfg.max_num_seqs)
     state = sum(int(torch.empty((), dtype=s.dtype).element_size()) * int(torch.Size(s.shape).numel())
-                for s in specs if isinstance(s, StateSpec))
+                for s in simple if isinstance(s, StateSpec))
     heads = [(getattr(p, "nh", 0), getattr(p, "d", 0)) for blk in model.blocks for p in blk.parts.values()]
-    slices = step_slices(cfg, model.hidden, model.vocab, el, workspace, len({s for s in specs if hasattr(s, "num_kv_heads")}),
+    slices = step_slices(cfg, model.hidden, model.vocab, el, workspace, len({s for s in simple if hasattr(s, "num_kv_heads")}),
                          max((h for h, _ in heads), default=0), max((d for _, d in heads), default=0), sm_count, state,
                          launches_per_step=8 * len(model.spec.run_order) + 4)
     weights = sum(t.numel() * t.element_size() for t in model.tensors())

@@ -30,7 +30,7 @@ from ..cache.manager import cdiv
 from ..config.engine_config import EngineConfig
 from .runner import StepEntry
 
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 4          # state slots; a trace holds no more live requests at a time
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, out=sys.stdout,

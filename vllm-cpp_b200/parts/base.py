@@ -26,9 +26,25 @@ class ParamSpec:
     role "matrix": a product's weight, held in the compute type, random N(0, std).
     role "bias":   added in float, held in float32, random N(0, std).
     role "gain":   a norm's scale, held in float32, random 1 + N(0, gain_std).
+    role "offset_gain": a norm's scale stored around zero (the part adds 1), held in float32, random N(0, gain_std).
+
+    A dimension of -1 is free: the checkpoint's tensor gives it (a table whose length no configuration key
+    names); ``default_shape`` is then what the random-weights mode makes.
     """
     shape: Tuple[int, ...]
     role: str = "matrix"
+    default_shape: Optional[Tuple[int, ...]] = None
+
+    def concrete_shape(self) -> Tuple[int, ...]:
+        if all(d >= 0 for d in self.shape):
+            return tuple(self.shape)
+        if self.default_shape is None:
+            raise ValueError(f"a tensor of shape {self.shape} has a free dimension and no default size")
+        return tuple(self.default_shape)
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w < 0 or w == g for w, g in zip(self.shape, shape))
 
 
 # -------------------------------------------------------------------- caches
@@ -49,6 +65,29 @@ class StateSpec:
     """Per-request state of fixed size, one slot per live request, zero at admission."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CompositeSpec:
+    """The cache needs of a mixer made of several (mixers side by side): one spec per member, in order.  The
+    cache manager serves each as if it were a cache layer of its own; the mixer receives a CompositeView."""
+    parts: Tuple[object, ...]
+
+
+def flatten_specs(specs) -> List[object]:
+    """The simple cache needs (PagedKVSpec, StateSpec) inside a list that may hold None and CompositeSpecs."""
+    out: List[object] = []
+    for s in specs:
+        if isinstance(s, CompositeSpec):
+            out.extend(flatten_specs(s.parts))
+        elif s is not None:
+            out.append(s)
+    return out
+
+
+@dataclass
+class CompositeView:
+    views: List[object]          # one view (PagedKVView, StateView or None) per member of the CompositeSpec
 
 
 @dataclass
@@ -216,6 +255,12 @@ class Norm(Part):
         Arrangements that norm what a sublayer returns call this; norms that cannot do it raise."""
         raise NotImplementedError(f"{type(self).__name__} cannot be applied to a sublayer's result")
 
+    def folded(self, factor: Optional[torch.Tensor]):
+        """(gain, eps) of the norm with ``factor`` (float32 [size] or None), which multiplies the normed row
+        coordinate by coordinate right after the norm, taken into the gain.  Norms that are not
+        x / sqrt(mean(x^2) + eps) * gain raise."""
+        raise NotImplementedError(f"{type(self).__name__} has no gain to fold a factor into")
+
     def split(self):
         """(gain, eps) if the norm is y = x * rsqrt(mean(x^2) + eps) * gain with a float32 gain vector:
         then the product before it may apply the gain and the product after it the per-row factor
@@ -267,6 +312,12 @@ class Gate(Part):
         raise NotImplementedError
 
 
+class Scale(Part):
+    """A learned factor per coordinate on a sublayer's result (a layer scale).  ``vector`` is the float32
+    tensor once loaded; the arrangement folds it into the gain of the norm before it (Norm.folded)."""
+    vector: Optional[torch.Tensor] = None
+
+
 class FeedForward(Part):
     def fuses_norm(self, n_tokens: int) -> bool:
         """As Mixer.fuses_norm."""
@@ -274,6 +325,11 @@ class FeedForward(Part):
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: StepContext, ws: Workspace) -> None:
         raise NotImplementedError
+
+
+class NormedInput:
+    """A value of ``pending`` (see Block.forward): ``delta`` already holds the next block's input, normed by the norm
+    that block starts with.  Only handed to a block whose ``accepts_normed`` named that norm."""
 
 
 class Block:
@@ -332,6 +388,11 @@ class Block:
         (``pending`` an ops.RowScale); None if it wants the residual stream as it is."""
         return None
 
+    def accepts_normed(self, n_tokens: int):
+        """(gain, eps) of the norm this block starts with if the block before may apply it itself and hand
+        the normed rows over in ``delta`` (``pending`` a NormedInput); None if the block runs its own norm."""
+        return None
+
     def forward(self, residual: torch.Tensor, delta: torch.Tensor, pending, step: StepContext,
                 cache, writes_cache: bool, ws: Workspace, next_block: "Optional[Block]" = None,
                 carry: Optional[torch.Tensor] = None, state: Optional[StateView] = None):
@@ -352,10 +413,11 @@ NORMS: Dict[str, Callable] = {}
 POSITION_ENCODINGS: Dict[str, Callable] = {}
 TOKEN_SHIFTS: Dict[str, Callable] = {}
 GATES: Dict[str, Callable] = {}
+SCALES: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
 # family name (the values of Block.SLOTS) -> registry of the parts of that family
 FAMILIES: Dict[str, Dict[str, Callable]] = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS,
-                                            "token_shift": TOKEN_SHIFTS, "gate": GATES}
+                                            "token_shift": TOKEN_SHIFTS, "gate": GATES, "scale": SCALES}
 
 
 def _register(table, name):
@@ -371,6 +433,7 @@ def register_norm(name): return _register(NORMS, name)
 def register_position_encoding(name): return _register(POSITION_ENCODINGS, name)
 def register_token_shift(name): return _register(TOKEN_SHIFTS, name)
 def register_gate(name): return _register(GATES, name)
+def register_scale(name): return _register(SCALES, name)
 def register_block(name): return _register(BLOCKS, name)
 
 

@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Block, register_block, workspace_piece
+from .base import Block, NormedInput, register_block, workspace_piece
 from .mlp import NoFeedForward
 
 
@@ -115,3 +115,67 @@ class ShiftGatePostNormBlock(Block):
             self.feed_forward_norm.add_normed(y, pre, self.feed_forward_gate.bias, residual, None, self.mult)
         ws.release(mark)
         return False
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and after each sublayer, and a learned factor per coordinate on what joins the stream:
+
+        x += mixer_scale * mixer_post_norm(mixer(mixer_norm(x)))
+        x += feed_forward_scale * feed_forward_post_norm(feed_forward(feed_forward_norm(x)))
+
+    The factor is folded into the post norm's gain at first use (Norm.folded).  Post norm, addition and the norm
+    before the next sublayer are one kernel (ops.norm_residual_norm): the one after the mixer prepares the
+    feed-forward's input, the one after the feed-forward the next layer's, when that layer is of this arrangement
+    too (NormedInput).  The residual stream is float32 throughout.  A layer whose feed-forward is "none" has only
+    the first line."""
+
+    SLOTS = {"mixer": "mixer", "feed_forward": "feed_forward",
+             "mixer_norm": "norm", "mixer_post_norm": "norm", "mixer_scale": "scale",
+             "feed_forward_norm": "norm", "feed_forward_post_norm": "norm", "feed_forward_scale": "scale"}
+
+    def __init__(self, params=None, **parts):
+        super().__init__(params=params, **parts)
+        self.has_ff = not isinstance(self.feed_forward, NoFeedForward)
+        self._gains = None
+
+    def _folded(self):
+        if self._gains is None:
+            self._gains = (self.mixer_post_norm.folded(self.mixer_scale.vector),
+                           self.feed_forward_post_norm.folded(self.feed_forward_scale.vector) if self.has_ff else None,
+                           self.feed_forward_norm.folded(None) if self.has_ff else None)
+        return self._gains
+
+    def accepts_normed(self, n_tokens):
+        return self.mixer_norm.folded(None)
+
+    def workspace_bytes(self, n_tokens, n_reqs, hidden, dtype):
+        return 2 * workspace_piece((n_tokens, hidden), dtype) + super().workspace_bytes(n_tokens, n_reqs, hidden, dtype)
+
+    def forward(self, residual, delta, pending, step, cache, writes_cache, ws, next_block=None, carry=None):
+        if isinstance(pending, ops.RowScale):
+            raise ValueError("sandwich_norm takes the residual stream as it is")
+        mark = ws.mark()
+        n, hidden = residual.shape
+        post_mixer, post_ff, pre_ff = self._folded()
+        y = ws.take((n, hidden), delta.dtype)
+        if isinstance(pending, NormedInput):
+            h = delta
+        else:
+            h = ws.take((n, hidden), delta.dtype)
+            self.mixer_norm.forward(residual, delta if pending else None, h)
+        self.mixer.forward(h, y, step, cache, writes_cache, ws)
+        after = next_block.accepts_normed(n) if next_block is not None else None
+        if self.has_ff:
+            ops.norm_residual_norm(y, post_mixer[0], residual, post_mixer[1], next_gain=pre_ff[0], next_out=h, next_eps=pre_ff[1])
+            self.feed_forward.forward(h, y, step, ws)
+            last = post_ff
+        else:
+            last = post_mixer
+        if after is None:
+            ops.norm_residual_norm(y, last[0], residual, last[1])
+            ws.release(mark)
+            return False
+        ops.norm_residual_norm(y, last[0], residual, last[1], next_gain=after[0], next_out=delta, next_eps=after[1])
+        ws.release(mark)
+        return NormedInput()

@@ -21,8 +21,9 @@ from ..config.model_spec import ModelSpec
 from ..csrc import ops
 from .base import BLOCKS, FAMILIES, NORMS, ParamSpec, StepContext, Workspace, build_part
 # importing the modules registers the built-in parts
-from . import (attention as _attention, block as _block, gate as _gate, latent_attention as _latent,  # noqa: F401
-               mlp as _mlp, norm as _norm, position as _position, shift as _shift)
+from . import (attention as _attention, biased_attention as _biased, block as _block, gate as _gate,  # noqa: F401
+               latent_attention as _latent, linear_attention as _linear, mlp as _mlp, moe as _moe, norm as _norm,
+               parallel as _parallel, position as _position, scale as _scale, shift as _shift)
 
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -198,6 +199,18 @@ class DecoderModel:
 
 
 MODEL_CLASSES["decoder"] = DecoderModel
+
+
+@register_model_class("scaled_embedding_decoder")
+class ScaledEmbeddingDecoderModel(DecoderModel):
+    """A decoder whose residual stream starts as  embedding * ``embedding_scale``  (ModelSpec.model_params)."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.embedding_scale = float(spec.model_params.get("embedding_scale", 1.0))
+
+    def embed_tokens(self, step, residual):
+        ops.embedding(self.embed, step.token_ids, residual, scale=self.embedding_scale)
 
 
 @register_model_class("scaled_sinusoid_decoder")

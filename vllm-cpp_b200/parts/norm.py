@@ -16,17 +16,25 @@ from .base import Norm, ParamSpec, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float, dtype, device):
+    """``tensor_name``: local name of the gain (""; the slot's prefix itself, for checkpoints that name the norm and
+    not a tensor inside it).  ``unit_offset``: the tensor is stored around zero and the gain is 1 + tensor."""
+
+    def __init__(self, size: int, eps: float, dtype, device, tensor_name: str = "weight", unit_offset: bool = False):
         if size <= 0 or not eps > 0:
             raise ValueError(f"rmsnorm: size {size} and eps {eps} must be positive")
         self.size, self.eps = size, float(eps)
+        self.tensor_name, self.unit_offset = tensor_name, bool(unit_offset)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), "gain")}
+        return {self.tensor_name: ParamSpec((self.size,), "offset_gain" if self.unit_offset else "gain")}
 
     def load_params(self, tensors):
-        self.weight = tensors["weight"]
+        w = tensors[self.tensor_name]
+        self.weight = (w + 1.0).contiguous() if self.unit_offset else w
+
+    def folded(self, factor):
+        return (self.weight if factor is None else (self.weight * factor).contiguous()), self.eps
 
     def split(self):
         return (self.weight, self.eps) if self.weight is not None and self.weight.dtype == torch.float32 else None

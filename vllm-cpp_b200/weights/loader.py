@@ -63,7 +63,7 @@ def check_names_and_shapes(expected: Dict[str, object], present: Dict[str, Tuple
                         and not any(n.endswith(s) for s in ignored_suffixes)
                         and n != tied_lm_head)
     wrong = sorted((n, tuple(present[n]), tuple(expected[n].shape)) for n in expected
-                   if n in present and tuple(present[n]) != tuple(expected[n].shape))
+                   if n in present and not expected[n].fits(present[n]))       # -1: the file gives that size
     if missing or unexpected or wrong:
         lines = ["checkpoint does not match the model:"]
         if missing:
@@ -79,7 +79,7 @@ def check_names_and_shapes(expected: Dict[str, object], present: Dict[str, Tuple
 def _place(t: torch.Tensor, role: str, compute_dtype: torch.dtype, device) -> torch.Tensor:
     if role == "matrix":
         target = compute_dtype
-    elif role in ("bias", "gain"):
+    elif role in ("bias", "gain", "offset_gain"):
         target = torch.float32
     elif t.dtype.is_floating_point:
         target = torch.float32 if (t.dtype == torch.float32 or compute_dtype == torch.float32) else torch.bfloat16

@@ -112,6 +112,8 @@ def normal_values(key: int, first: int, count: int, mean: float, std: float) -> 
 
 
 def _mean_std(role: str, std: float, gain_std: float):
+    if role == "offset_gain":
+        return 0.0, gain_std
     return (1.0, gain_std) if role == "gain" else (0.0, std)
 
 
@@ -159,7 +161,7 @@ def write_random_model(path: str, config: dict, seed: int = 0, dtype: str = "bfl
     gain_std = spec.init_gain_std if gain_std is None else gain_std
     tensors = {}
     for name, ps in model.param_specs().items():
-        tensors[name] = random_tensor(name, ps.shape, ps.role, seed, std, gain_std,
+        tensors[name] = random_tensor(name, ps.concrete_shape(), ps.role, seed, std, gain_std,
                                       dtype=TORCH_DTYPES[dtype], device=device).cpu()
     os.makedirs(path, exist_ok=True)
     with open(os.path.join(path, "config.json"), "w") as f:
@@ -181,8 +183,8 @@ def init_random_on_device(model, seed: int, std: Optional[float] = None,
         held = model.placement(ps.role)
         if held == torch.float32 and model.dtype != torch.float32:
             # a bias or gain of a bfloat16 model: the value a bfloat16 checkpoint would hold, kept in float32
-            t = random_tensor(name, ps.shape, ps.role, seed, std, gain_std, dtype=model.dtype, device=model.device).to(held)
+            t = random_tensor(name, ps.concrete_shape(), ps.role, seed, std, gain_std, dtype=model.dtype, device=model.device).to(held)
         else:
-            t = random_tensor(name, ps.shape, ps.role, seed, std, gain_std, dtype=held, device=model.device)
+            t = random_tensor(name, ps.concrete_shape(), ps.role, seed, std, gain_std, dtype=held, device=model.device)
         tensors[name] = t
     model.load_params(tensors)
