@@ -155,24 +155,35 @@ def distance_bucket(n, rows, reach):
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(reach / half) * (rows - half))))
 
 
-def biased_window_attention(w, p, m, h, eps):
-    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    W, cap, scale, reach = m["mask"]["size"], m["softcap"], m["scale"], m["bias_max"]
-    rel = w[p + "rel"]
-    T = h.shape[0]
-    q = plain_norm(h @ w[p + "q"].T, w[p + "q.norm"], eps)
-    k = plain_norm(h @ w[p + "k"].T, w[p + "k.norm"], eps)
-    v = h @ w[p + "v"].T
+def capped_biased_attention(q, k, v, rel, H, G, W, cap, scale, reach):
+    """q [T, H*d], k [T, G*d], v [T, G*e] of one sequence -> [T, H*e]: capped scores plus the bias of the distance,
+    softmax over the keys j with 0 <= i - j < W (W 0: all j <= i)."""
+    T = q.shape[0]
+    d, e = q.shape[1] // H, v.shape[1] // G
     out = np.zeros((T, H * e))
+    far = T if not W else min(T, W)
+    buckets = np.array([distance_bucket(n, rel.shape[0], reach) for n in range(far)], dtype=np.int64)
     for head in range(H):
         g = head // (H // G)
         for i in range(T):
-            lo = max(0, i - W + 1)
-            s = np.array([cap * math.tanh(scale * (q[i, head * d:(head + 1) * d] @ k[j, g * d:(g + 1) * d]) / cap)
-                          + rel[distance_bucket(i - j, rel.shape[0], reach), head] for j in range(lo, i + 1)])
+            lo = max(0, i - W + 1) if W else 0
+            s = scale * (k[lo:i + 1, g * d:(g + 1) * d] @ q[i, head * d:(head + 1) * d])
+            if cap:
+                s = cap * np.tanh(s / cap)
+            s = s + rel[buckets[i - np.arange(lo, i + 1)], head]
             pr = np.exp(s - s.max())
             pr /= pr.sum()
             out[i, head * e:(head + 1) * e] = pr @ v[lo:i + 1, g * e:(g + 1) * e]
+    return out
+
+
+def biased_window_attention(w, p, m, h, eps):
+    W = m["mask"]["size"] if m.get("mask") else 0            # 0: every earlier key is seen
+    q = plain_norm(h @ w[p + "q"].T, w[p + "q.norm"], eps)
+    k = plain_norm(h @ w[p + "k"].T, w[p + "k.norm"], eps)
+    v = h @ w[p + "v"].T
+    out = capped_biased_attention(q, k, v, w[p + "rel"], m["heads"], m["kv_heads"], W, m.get("softcap", 0.0), m["scale"],
+                                  m["bias_max"])
     return (out * sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
 
 
@@ -204,20 +215,25 @@ def clamped_expert(w, p, h, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
-def route(w, p, r, h):
-    """(chosen [T, top], weights [T, top]) over experts + identity outputs."""
+def route(w, p, r, h, margins=None):
+    """(chosen [T, top], weights [T, top]) over experts + identity outputs.  ``margins`` (a list) receives, per
+    token, how far the last chosen output's choice score lies above the best one left out."""
     z = h @ w[p + "router"].T
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z)
     s /= s.sum(axis=-1, keepdims=True)
     choice = s + w[p + "correction"]
-    chosen = np.argsort(-choice, axis=-1, kind="stable")[:, : r["top"]]
+    order = np.argsort(-choice, axis=-1, kind="stable")
+    chosen = order[:, : r["top"]]
+    if margins is not None and order.shape[1] > r["top"]:
+        ranked = np.take_along_axis(choice, order, axis=-1)
+        margins.extend(ranked[:, r["top"] - 1] - ranked[:, r["top"]])
     return chosen, np.take_along_axis(s, chosen, axis=-1)
 
 
-def moe_ff(w, p, mlp, h):
+def moe_ff(w, p, mlp, h, margins=None):
     r = mlp["router"]
-    chosen, weights = route(w, p, r, h)
+    chosen, weights = route(w, p, r, h, margins)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for c, wt in zip(chosen[t], weights[t]):
@@ -228,7 +244,7 @@ def moe_ff(w, p, mlp, h):
     return out
 
 
-def forward(cfg, w, tokens, return_layers=False):
+def forward(cfg, w, tokens, return_layers=False, margins=None):
     eps = cfg["norm"]["eps"]
     x = w["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
     layers = []
@@ -245,7 +261,7 @@ def forward(cfg, w, tokens, return_layers=False):
         mlp = layer.get("mlp")
         if mlp is not None:
             h = layer_norm(x, w[p + "norm2"], eps)
-            y = dense_ff(w, p + "mlp.", h) if mlp["kind"] == "dense" else moe_ff(w, p + "mlp.", mlp, h)
+            y = dense_ff(w, p + "mlp.", h) if mlp["kind"] == "dense" else moe_ff(w, p + "mlp.", mlp, h, margins)
             x = x + w[p + "ls2"] * layer_norm(y, w[p + "norm2b"], eps)
         layers.append(x.copy())
     logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T
@@ -254,6 +270,14 @@ def forward(cfg, w, tokens, return_layers=False):
 
 def greedy(logits_row):
     return int(np.argmax(logits_row))
+
+
+def routing_margin(cfg, w, tokens):
+    """The smallest margin of any routing decision on these tokens (inf without routed layers): a test that
+    compares logits asks for tokens whose decisions rounding cannot turn."""
+    margins = []
+    forward(cfg, w, tokens, margins=margins)
+    return min(margins) if margins else math.inf
 
 
 # ------------------------------------------------------------ random models
@@ -294,10 +318,14 @@ def tensor_shapes(cfg):
     return s
 
 
-def random_weights(cfg, seed, std=None, sharp=1.0):
+def random_weights(cfg, seed, std=None, sharp=1.0, decisive_routing=False):
     """Random weights for a configuration made by the tests ('rel_rows' in a left mixer and 'decay_rank' in a gla
     mixer are the tests' own keys: the engine reads those sizes from the tensors).  ``sharp`` scales the
-    left mixers' q and k gains, so that their softmax is peaked."""
+    left mixers' q and k gains, so that their softmax is peaked.  ``decisive_routing``: the routers' corrections lie
+    0.4 apart in a random order, so that no rounding of the scores turns a choice (the weights still follow the scores).
+    In a gla mixer the key matrix is the query matrix plus noise: a head's result is normed by itself, and at a
+    sequence's first token it is v_0 (k_0 . q_0), whose sign would hang on the rounding of one dot product of
+    unrelated vectors; with related ones the product is clearly positive and the comparison means something."""
     rng = np.random.default_rng(seed)
     W = cfg["width"]
     std = std if std is not None else 1.0 / math.sqrt(W)
@@ -315,7 +343,7 @@ def random_weights(cfg, seed, std=None, sharp=1.0):
         elif leaf == "rel":
             w[name] = rng.standard_normal(shape)
         elif leaf == "correction":
-            w[name] = 0.05 * rng.standard_normal(shape)
+            w[name] = 0.4 * rng.permutation(shape[0]) if decisive_routing else 0.05 * rng.standard_normal(shape)
         elif name.endswith("a2.b"):
             w[name] = 2.0 + rng.standard_normal(shape)
         elif name.endswith(".a2"):
@@ -326,4 +354,7 @@ def random_weights(cfg, seed, std=None, sharp=1.0):
             w[name] = rng.standard_normal(shape) * std
         else:
             w[name] = rng.standard_normal(shape) * std
+    for i, layer in enumerate(cfg["layers"]):
+        if layer["type"] == "gla":
+            w[f"l{i}.mix.k"] = w[f"l{i}.mix.q"] + 0.5 * w[f"l{i}.mix.k"]
     return w

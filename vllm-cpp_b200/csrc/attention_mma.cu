@@ -57,7 +57,28 @@ struct MmaAttnArgs {
     int kv_share;                  // decode: this many consecutive kv heads of `nkv` are one head of the cache.  A group of more
                                    // than 16 query heads is cut into equal groups of at most 16 that run as CTAs of their own
                                    // instead of as passes of one CTA over the same keys (1: nkv is the cache's own count)
+    // Shaped scores (all zero: plain scaled scores).  score = cap * tanh(scale * q.k / cap) (cap > 0), then
+    // + bias_t[head * bias_len + min(distance, bias_len - 1)] (bias_t not null), distance = query position - key position.
+    float cap;
+    const float* bias_t;           // [nh][bias_len]: a head's bias by distance, contiguous
+    int bias_len;
 };
+
+// tanh through one ex2 and one division: absolute error of a few 1e-7, which is what a capped score needs
+// (tanh.approx is good to 2^-11 only, times the cap).
+__device__ __forceinline__ float tanh_ex2(float x) {
+    return 1.0f - __fdividef(2.0f, 1.0f + exp2f(x * 2.8853900817779268f));
+}
+
+// A raw product q.k into the score the softmax sees.  `dist` is clamped into the bias table; keys that the mask
+// removes afterwards may come with any distance.
+__device__ __forceinline__ float shaped_score(float raw, float scale, float cap, float inv_cap, const float* bias_row,
+                                              int dist, int bias_len) {
+    float x = raw * scale;
+    if (cap > 0.0f) x = cap * tanh_ex2(x * inv_cap);
+    if (bias_row) x += __ldg(bias_row + min(max(dist, 0), bias_len - 1));
+    return x;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -264,7 +285,9 @@ attention_decode_kernel(MmaAttnArgs a) {
     const int hi = pos + 1;
     const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
-    const float sl2 = a.scale * LOG2E;                   // scores in units of log2
+    const bool shaped = a.cap > 0.0f || a.bias_t != nullptr;
+    const float sl2 = (shaped ? 1.0f : a.scale) * LOG2E; // scores in units of log2 (shaped scores carry the scale already)
+    const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
     // The splits of a request.  With split_tiles no split of any request has more than that many tiles
     // (a request's tiles are dealt evenly to the splits it needs), so a request with a long context gets
@@ -347,6 +370,19 @@ attention_decode_kernel(MmaAttnArgs a) {
 #pragma unroll
                 for (int i = 0; i < 2; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
                 qk_product<D, BN, 2>(s, qf, sk, warp * 16);
+                if (shaped) {
+                    // rows lane / 4 and lane / 4 + 8 of the fragment are heads of the group
+                    const int ha = g * G + min(mt * 16 + (lane >> 2), G - 1), hb = g * G + min(mt * 16 + (lane >> 2) + 8, G - 1);
+                    const float* ba = a.bias_t ? a.bias_t + (size_t)ha * a.bias_len : nullptr;
+                    const float* bb = a.bias_t ? a.bias_t + (size_t)hb * a.bias_len : nullptr;
+#pragma unroll
+                    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
+                            s[nb][e] = shaped_score(s[nb][e], a.scale, a.cap, inv_cap, e < 2 ? ba : bb, pos - j, a.bias_len);
+                        }
+                }
                 // only a tile that crosses lo or hi has keys to mask (the same for the whole CTA)
                 if (tile * BN < lo || tile * BN + BN > hi) {
 #pragma unroll
@@ -643,7 +679,9 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     const int q0 = a.q_start[r], q_len = a.q_start[r + 1] - q0, ctx = a.ctx_lens[r];
     const int rows_total = q_len * G;
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
-    const float sl2 = a.scale * LOG2E;
+    const bool shaped = a.cap > 0.0f || a.bias_t != nullptr;
+    const float sl2 = (shaped ? 1.0f : a.scale) * LOG2E;
+    const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
 
     // [Q][K stages][V stages][barriers]
     const uint32_t sq = smem_u32(smem), sk0 = sq + Q_BYTES, sv0 = sk0 + K_STAGES * KV_BYTES;
@@ -813,6 +851,8 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
         const bool row_ok = pr < rows_total;
         const int pos = ctx + min(pr, rows_total - 1) / G;                 // the row's position
         const int row_lo = a.window > 0 ? max(0, pos + 1 - a.window) : 0;
+        // the row's head, for the bias by distance
+        const float* bias_row = a.bias_t ? a.bias_t + (size_t)(g * G + min(pr, rows_total - 1) % G) * a.bias_len : nullptr;
         float m_ref = -INFINITY, l = 0.0f;           // the exponent's reference (in raw score units) and the sum relative to it
         bool ok = true;
         for (int j = 0; j < n_tiles && !*abort_flag; ++j) {
@@ -837,6 +877,10 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             __syncwarp();
             if (lane == 0) cx_mbar_arrive(B(S_FREE + st));
             float mt = -INFINITY;
+            if (shaped) {
+#pragma unroll
+                for (int i = 0; i < TKT; ++i) s[i] = shaped_score(s[i], a.scale, a.cap, inv_cap, bias_row, pos - (kb + i), a.bias_len);
+            }
             if (edge) {
 #pragma unroll
                 for (int i = 0; i < TKT; ++i) {
@@ -976,6 +1020,25 @@ VCB_EXPORT int vcb_attention_decode_mma_planes(const void* q, const void* cache,
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
 
+// The same with shaped scores (see MmaAttnArgs): cap <= 0 no cap, bias_t null no bias.
+VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* req_list, int n_list, int nsplit, float* part_o,
+                                               float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
+                                               int d, int page, int window, float scale, int num_pages, int* status,
+                                               int kv_share, float cap, const float* bias_t, int bias_len, void* stream) {
+    if (n_list <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window, num_pages);
+    if (c) return c;
+    if (kv_share < 1 || nkv % kv_share || (bias_t && bias_len <= 0)) return VCB_ERR_BAD_ARG;
+    if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
+                  page, window, scale, num_pages, 2, kv_share, cap, bias_t, bias_len};
+    cudaStream_t s = (cudaStream_t)stream;
+    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+}
+
 VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* out, const int* q_start,
                                         const int* ctx_lens, const int* block_table, int bt_stride,
                                         const int* req_list, int n_list, int nsplit, float* part_o,
@@ -1002,6 +1065,22 @@ VCB_EXPORT int vcb_attention_prefill_tc_planes(const void* q, const void* cache,
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
                   window, scale, num_pages, planes, 1};
+    return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
+}
+
+// The same with shaped scores (see MmaAttnArgs).
+VCB_EXPORT int vcb_attention_prefill_tc_shaped(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* tile_req, const int* tile_row0, int n_tiles, int nh,
+                                               int nkv, int d, int page, int window, float scale, int num_pages,
+                                               int* status, float cap, const float* bias_t, int bias_len, void* stream) {
+    if (n_tiles <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window, num_pages);
+    if (c) return c;
+    if (bias_t && bias_len <= 0) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
+                  window, scale, num_pages, 2, 1, cap, bias_t, bias_len};
     return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 

@@ -54,6 +54,8 @@ _SIGNATURES = {
     "vcb_latent_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, ctypes.c_longlong, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I, _P],
+    "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P],
     "vcb_embedding_scaled": [_P, _P, _P, _I, _I, _I, _P, _F, _I, _P],
     "vcb_norm_residual_norm": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P],
     "vcb_decayed_state_scan": [_P, _P, _P, _P, _L, _L, _L, _L, _P, _P, _F, _F, _I, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -261,7 +263,8 @@ DECODE_MAX_SPLITS = 32
 
 def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
                          part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                         window: int, scale: float, split_tiles=None, planes: int = 2, kv_share: int = 1) -> None:
+                         window: int, scale: float, split_tiles=None, planes: int = 2, kv_share: int = 1,
+                         cap: float = 0.0, bias_t: Optional[torch.Tensor] = None) -> None:
     """Split-KV tensor-core attention for requests that bring one token each (bfloat16).  The grid has
     ``nsplit`` columns; without ``split_tiles`` every request's keys are cut into that many equal parts,
     with it (int32 [1] on the device: tiles of DECODE_KEY_TILE keys per split) a request takes as many
@@ -279,6 +282,23 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
               "attention_decode_mma: scratch for the split merge is too small")
     _need(planes in (1, 2), "planes must be 1 or 2")
     _need(kv_share >= 1 and num_kv_heads % kv_share == 0, "attention_decode_mma: kv_share divides num_kv_heads")
+    if cap > 0 or bias_t is not None:
+        # shaped scores: cap * tanh(scale * q.k / cap) + bias_t[head, min(distance, last)] (see attention_mma.cu)
+        _need(planes == 2, "attention_decode_mma: shaped scores come with keys and values in planes of their own")
+        _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_decode_mma: bias_t [heads, distances]")
+        _check(lib().vcb_attention_decode_mma_shaped(
+            _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
+            _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
+            block_table.shape[1], None if req_list is None else _dev(req_list, "req_list", torch.int32),
+            n_list, nsplit, None if part_o is None else _dev(part_o, "part_o", torch.float32),
+            None if part_ml is None else _dev(part_ml, "part_ml", torch.float32),
+            None if counters is None else _dev(counters, "counters", torch.int32),
+            None if split_tiles is None else _dev(split_tiles, "split_tiles", torch.int32),
+            num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
+            status_tensor(q.device).data_ptr(), kv_share, float(cap),
+            None if bias_t is None else _dev(bias_t, "bias_t", torch.float32), 0 if bias_t is None else bias_t.shape[1],
+            _stream()), "attention_decode_mma")
+        return
     _check(lib().vcb_attention_decode_mma_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
@@ -308,7 +328,7 @@ TC_ATTENTION_TILE_ROWS = 128     # packed rows per tile of its work list
 
 def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                         scale: float, planes: int = 2) -> None:
+                         scale: float, planes: int = 2, cap: float = 0.0, bias_t: Optional[torch.Tensor] = None) -> None:
     """Attention for portions of any length on tcgen05 tensor cores (scores and output tiles in tensor
     memory); head sizes 64 and 128, bfloat16, pages of a multiple of 8 slots, tiles of 128 packed rows."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -318,6 +338,17 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
     n_tiles = tile_req.numel()
     _need(tile_row0.numel() == n_tiles, "one first row per tile")
     _need(planes in (1, 2), "planes must be 1 or 2")
+    if cap > 0 or bias_t is not None:
+        _need(planes == 2, "attention_prefill_tc: shaped scores come with keys and values in planes of their own")
+        _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_prefill_tc: bias_t [heads, distances]")
+        _check(lib().vcb_attention_prefill_tc_shaped(
+            _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
+            _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
+            block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
+            n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
+            status_tensor(q.device).data_ptr(), float(cap), None if bias_t is None else _dev(bias_t, "bias_t", torch.float32),
+            0 if bias_t is None else bias_t.shape[1], _stream()), "attention_prefill_tc")
+        return
     _check(lib().vcb_attention_prefill_tc_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
@@ -1071,6 +1102,14 @@ def headwise_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: O
     _check(lib().vcb_headwise_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), None if gate is None else gate.data_ptr(),
                                      n, heads, N, K, x.stride(0), out.stride(0), 0 if gate is None else gate.stride(0),
                                      dtype_code(x.dtype), _stream()), "headwise_linear")
+
+
+def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> None:
+    """out *= sigmoid(gate) in place; rows of both may be strided."""
+    n, cols = out.shape
+    _need(gate.shape == out.shape and gate.dtype == out.dtype and out.stride(1) == 1 and gate.stride(1) == 1, "sigmoid_gate: gate like out")
+    _check(lib().vcb_sigmoid_gate(out.data_ptr(), gate.data_ptr(), n, cols, out.stride(0), gate.stride(0),
+                                  dtype_code(out.dtype), _stream()), "sigmoid_gate")
 
 
 def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:

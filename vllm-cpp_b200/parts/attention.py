@@ -125,10 +125,15 @@ class PagedAttentionKernels(Mixer):
     def _splits_key(self):
         return f"attn_splits_kv{self.decode_groups()}_w{self.window}"
 
+    def score_shaping(self) -> dict:
+        """What the tensor-core kernels do to a score beyond the scale: ``cap`` (cap * tanh(score / cap)) and ``bias_t``
+        (float32 [heads, distances], added by distance); empty for plain scaled scores."""
+        return {}
+
     def attend(self, q, attn, step, cache, block_table):
         if self._tensor_core_path():
             kw = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size,
-                      window=self.window, scale=self.scale, planes=self.planes)
+                      window=self.window, scale=self.scale, planes=self.planes, **self.score_shaping())
             if step.decode_only:
                 nsplit = step.shapes.get(self._splits_key())
                 split_tiles = step.extras.get(self._splits_key())

@@ -15,6 +15,9 @@ kernel looks a distance up directly.  ``cap`` 0 switches the cap off, ``window``
 
 The cache holds the normed keys and the values in rows of max(head_dim, v_head_dim) elements
 (PagedKVSpec.head_dim); with a window, pages behind it are given back.  q, k, v and the gate are one product.
+In bfloat16 with key and value heads of one size, 64 or 128, attention runs on the engine's tensor-core kernels
+(tcgen05 for portions, mma.sync split over the keys for single tokens), which cap and bias the scores inside their
+softmax; other sizes and float32 run the plain kernel of csrc/attention_biased.cu.
 The reference's attention (src/layers/attention.cpp) has rotation and none of the rest.
 """
 from __future__ import annotations
@@ -26,7 +29,8 @@ import numpy as np
 import torch
 
 from ..csrc import ops
-from .base import Mixer, PagedKVSpec, ParamSpec, register_mixer, workspace_piece
+from .attention import PagedAttentionKernels
+from .base import PagedKVSpec, ParamSpec, register_mixer, workspace_piece
 
 DEFAULT_BIAS_ROWS = 32       # rows of the bias table where no checkpoint gives them (random weights)
 
@@ -44,7 +48,7 @@ def distance_buckets(rows: int, reach: float, count: int) -> np.ndarray:
 
 
 @register_mixer("biased_window_attention")
-class BiasedWindowAttention(Mixer):
+class BiasedWindowAttention(PagedAttentionKernels):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float,
                  softcap: float, window: int, bias_reach: float, eps: float, dtype, device, qk_norm: bool = True,
                  output_gate: bool = True):
@@ -56,10 +60,11 @@ class BiasedWindowAttention(Mixer):
             raise ValueError("biased_window_attention: window and softcap must not be negative, eps and bias_reach positive")
         self.hidden, self.nh, self.nkv, self.dk, self.dv = hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim
         self.row = max(head_dim, v_head_dim)
+        self.d = self.row              # a cached row's width, as the paged attention kernels see it
         self.scale, self.cap, self.window, self.reach, self.eps = float(scale), float(softcap), int(window), float(bias_reach), float(eps)
         self.qk_norm, self.output_gate = bool(qk_norm), bool(output_gate)
         self.dtype, self.device = dtype, device
-        self.w_in = self.w_o = self.w_qn = self.w_kn = self.bias = None
+        self.w_in = self.w_o = self.w_qn = self.w_kn = self.bias = self.bias_t = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         q, kk, vv = self.nh * self.dk, self.nkv * self.dk, self.nkv * self.dv
@@ -88,7 +93,16 @@ class BiasedWindowAttention(Mixer):
         if self.window > 0:
             count = min(count, self.window)
         idx = torch.from_numpy(distance_buckets(B, self.reach, count)).to(rel.device)
-        self.bias = rel.index_select(0, idx).contiguous()
+        self.bias = rel.index_select(0, idx).contiguous()           # [distances, heads]
+        self.bias_t = self.bias.t().contiguous()                    # [heads, distances], for the tensor-core kernels
+        if self.dk == self.dv:
+            self.warn_if_plain()
+
+    def _tensor_core_path(self) -> bool:
+        return self.dk == self.dv and super()._tensor_core_path()
+
+    def score_shaping(self):
+        return {"cap": self.cap, "bias_t": self.bias_t}
 
     def product_weights(self):
         return [(self.w_in, 0), (self.w_o, 0)]
@@ -119,7 +133,13 @@ class BiasedWindowAttention(Mixer):
         ops.qk_norm_cache_write(proj, q_off, k_off, v_off, self.w_qn, self.w_kn, q, pages, step.positions, step.req_of_token,
                                 block_table, eps=self.eps, write_kv=writes_cache, **sizes)
         attn = ws.take((n, self.nh * self.dv), self.dtype)
-        ops.attention_biased(q, pages, attn, proj[:, g_off:] if self.output_gate else None, step.positions, step.req_of_token,
-                             block_table, self.bias, window=self.window, scale=self.scale, cap=self.cap, **sizes)
+        gate = proj[:, g_off:] if self.output_gate else None
+        if self._tensor_core_path() and cache.page_size % 8 == 0:
+            self.attend(q, attn, step, cache, block_table)
+            if gate is not None:
+                ops.sigmoid_gate(attn, gate)
+        else:
+            ops.attention_biased(q, pages, attn, gate, step.positions, step.req_of_token, block_table, self.bias,
+                                 window=self.window, scale=self.scale, cap=self.cap, **sizes)
         ops.linear(attn, self.w_o, out)
         ws.release(mark)
