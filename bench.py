@@ -658,6 +658,325 @@ def rolesun_kernels(z, peaks):
     return rows
 
 
+# ------------------------------------------------------------------- the Retodra design beside Qwen2
+# Layer sizes that resemble real models'.  Retodra: layers of gated linear attention with a dense feed-forward in turn
+# with layers of windowed attention (capped scores, bias by distance) beside lightning attention with routed experts.
+# Qwen2 at equal width, heads, kv heads, head size, window and dense feed-forward width is the nearest model the
+# engine has.
+RETODRA_SIZES = {"2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, experts=16, top=2, expert_ff=2048, layers=4),
+                 "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, experts=32, top=4, expert_ff=2048, layers=4)}
+RETODRA_VOCAB, RETODRA_CONTEXT, RETODRA_PROMPT, RETODRA_WINDOW = 32000, 2048, 2048, 1024
+
+
+def retodra_configs(size):
+    z = RETODRA_SIZES[size]
+    w, h = z["width"], z["heads"]
+    gla = {"type": "gla", "mixer": {"heads": h, "dim": 64, "vdim": w // h, "tau": 16.0}, "mlp": {"kind": "dense", "ff": z["ff"]}}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": h, "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                              "softcap": 30.0, "bias_max": float(RETODRA_WINDOW), "mask": {"size": RETODRA_WINDOW}},
+                     "right": {"heads": h, "dim": 64, "vdim": w // h, "decay": [1.0 - 2.0 ** (-5 - 3 * i / h) for i in range(h)]},
+                     "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+                   "router": {"experts": z["experts"], "identity": 1, "top": z["top"]}}}
+    retodra = {"architecture": "Retodra", "vocab": RETODRA_VOCAB, "width": w, "embedding": {"scale": float(w) ** 0.5},
+               "norm": {"eps": 1e-6}, "layers": [dict(gla if i % 2 == 0 else par) for i in range(z["layers"])]}
+    qwen = dict(QWEN25_7B, hidden_size=w, num_hidden_layers=z["layers"], num_attention_heads=h, num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], intermediate_size=z["ff"], vocab_size=RETODRA_VOCAB, use_sliding_window=True,
+                sliding_window=RETODRA_WINDOW, max_window_layers=0)
+    return retodra, qwen
+
+
+def decode_step_bytes(model, cache, batch, context):
+    """Bytes a decode step of ``batch`` requests with ``context`` cached tokens must move: every weight matrix once (of
+    routed experts only as many as the step's tokens can reach), the cached rows inside each layer's window, and every
+    request's recurrent state in and out."""
+    from vllm_cpp_b200.parts.base import PagedKVSpec, StateSpec, flatten_specs
+    total = 0
+    seen = set()
+
+    def walk(part):
+        nonlocal total
+        for v in vars(part).values():
+            if hasattr(v, "data_ptr") and v.data_ptr() not in seen and v is not model.embed:
+                seen.add(v.data_ptr())
+                nbytes = v.numel() * v.element_size()
+                if v.dim() == 3 and hasattr(part, "top"):                     # stacked experts
+                    nbytes = nbytes * min(v.shape[0], batch * part.top) // v.shape[0]
+                total += nbytes
+            elif hasattr(v, "param_specs"):
+                walk(v)
+    for blk in model.blocks:
+        for part in blk.parts.values():
+            walk(part)
+    walk(model.final_norm)
+    total += model.lm_head.numel() * model.lm_head.element_size()
+    el = model.embed.element_size()
+    for spec in flatten_specs(model.cache_specs()):
+        if isinstance(spec, PagedKVSpec):
+            keys = min(context, spec.window) if spec.window else context
+            total += batch * keys * spec.planes * spec.num_kv_heads * spec.head_dim * el
+        elif isinstance(spec, StateSpec):
+            n = 4
+            for d in spec.shape:
+                n *= d
+            total += 2 * batch * n
+    return total
+
+
+def measure_design(cfg, batches, steps, warmup, rng, peaks, vocab, context, prompt):
+    """Prefill of one prompt and decode steps of a design's engine on synthetic cache contents: device time by CUDA
+    events around the engine's step function (decode steps replay captured graphs, sampling included)."""
+    import torch
+    from vllm_cpp_b200 import EngineConfig
+    from vllm_cpp_b200.csrc import ops
+    from vllm_cpp_b200.engine.llm_engine import Engine
+    from vllm_cpp_b200.engine.runner import StepEntry
+    max_batch = max(batches)
+    ctx_room = context + steps + warmup + 64
+    pages = max_batch * (ctx_room // 16 + 1) + prompt // 16 + 16
+    engine = Engine(EngineConfig(load_format="random", model_config=cfg, seed=0, dtype="bfloat16", block_size=16,
+                                 num_gpu_blocks=pages, max_num_seqs=max_batch, max_model_len=ctx_room,
+                                 max_num_batched_tokens=prompt, max_tokens_per_step=prompt))
+    runner, cache, model = engine.runner, engine.cache, engine.model
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    for g in cache.paged:
+        g.pages.normal_(0.0, 0.5, generator=gen)
+    res = {"weight_gb": round(sum(t.numel() * t.element_size() for t in model.tensors() if t is not model.embed) / 1e9, 3)}
+    times = []
+    for k in range(warmup + 3):
+        cache.add_request("p")
+        toks = rng.integers(0, vocab, size=prompt).tolist()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry("p", toks, [prompt - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        cache.free_request("p")
+        if k >= warmup:
+            times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    res["prefill"] = {"tokens": prompt, "ms": round(ms, 3), "tok_s": round(prompt / ms * 1e3)}
+    res["decode"] = {}
+    for batch in batches:
+        temperature, uniform = torch.zeros(batch, device="cuda"), torch.zeros(batch, device="cuda")
+        ids_out = torch.empty(batch, dtype=torch.int32, device="cuda")
+        toks = rng.integers(0, vocab, size=(steps + warmup, batch))
+        ids = [f"d{batch}_{i}" for i in range(batch)]
+        for r in ids:
+            cache.add_request(r)
+            cache.reserve(r, context)
+            cache.commit(r, context)
+
+        def one(j):
+            logits = runner.step([StepEntry(r, [int(toks[j, i])], [0]) for i, r in enumerate(ids)])
+            ops.sample(logits, temperature, uniform, ids_out)
+
+        for j in range(warmup):
+            one(j)
+        torch.cuda.synchronize()
+        before = ops.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for j in range(warmup, warmup + steps):
+            one(j)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        bytes_ = decode_step_bytes(model, cache, batch, context + warmup + steps // 2)
+        res["decode"][str(batch)] = {"ms_per_step": round(ms, 4), "tok_s": round(batch / ms * 1e3), "gb_per_step": round(bytes_ / 1e9, 3),
+                                     "of_hbm_peak": round(bytes_ / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3),
+                                     "launches_per_step": (ops.launch_count() - before) // steps}
+        for r in ids:
+            cache.free_request(r)
+    ops.check_status()
+    del engine, runner, cache, model
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_retodra(a) -> int:
+    """Prefill and decode throughput of the Retodra design beside Qwen2 at equal layer sizes (random weights, synthetic
+    cache contents), and the design's own kernels alone beside the like kernels of Qwen2's layer with their share of the
+    measured peaks.  One JSON line."""
+    import numpy as np
+    peaks = load_peaks()
+    steps, warmup = max(1, a.steps), max(3, a.warmup)
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sampler.mark("decode")
+    out = {"metric": "prefill and decode tok/s of Retodra beside Qwen2 at equal layer sizes (bf16, random weights)",
+           "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic", "sizes": {}, "peaks": peaks}
+    sizes = a.retodra.split(",") if a.retodra != "all" else sorted(RETODRA_SIZES)
+    for size in sizes:
+        retodra, qwen = retodra_configs(size)
+        args = (steps, warmup, rng, peaks, RETODRA_VOCAB, RETODRA_CONTEXT, RETODRA_PROMPT)
+        out["sizes"][size] = {"layers": RETODRA_SIZES[size], "retodra": measure_design(retodra, (8, 64), *args),
+                              "qwen2_windowed": measure_design(qwen, (8, 64), *args)}
+    out["kernels"] = retodra_kernels(RETODRA_SIZES[sizes[-1]], peaks)
+    out["clocks"] = sampler.stop()
+    big = out["sizes"][sizes[-1]]
+    out.update(value=big["retodra"]["decode"]["8"]["tok_s"], unit=f"tokens/s (Retodra, {sizes[-1]}-wide layers, batch 8)",
+               higher_is_better=True, gpu_launches=big["retodra"]["decode"]["8"]["launches_per_step"] * steps,
+               config={"sizes": RETODRA_SIZES, "context": RETODRA_CONTEXT, "prompt": RETODRA_PROMPT, "window": RETODRA_WINDOW,
+                       "l2": "a step's weights exceed the 126 MB of L2"})
+    print(json.dumps(out))
+    return 0
+
+
+def retodra_kernels(z, peaks):
+    """The design's own kernels alone at one layer size, each beside the like kernel of Qwen2's layer:
+    [{kernel, like, us, GB/s or TFLOP/s, share of the measured peak}, ...] (CUDA graphs on rotating buffers)."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.config.model_spec import PartSpec
+    from vllm_cpp_b200.csrc import ops
+    from vllm_cpp_b200.engine.runner import HostStep
+    from vllm_cpp_b200.parts.attention import PagedAttention
+    h, nh, nkv, d, page, bf, dev = z["width"], z["heads"], z["kv_heads"], z["dim"], 16, torch.bfloat16, "cuda"
+    dk, dv, W = 64, h // nh, RETODRA_WINDOW
+    rows = []
+
+    def rnd(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, device=dev) * scale).to(dtype)
+
+    def add(name, like, fn, copies, bytes_=0, flops=0):
+        us = ops.time_in_graph(fn, reps=max(4, copies))
+        rate = bytes_ / us / 1e3 if bytes_ else flops / us / 1e6
+        rows.append({"kernel": name, "like": like, "us": round(us, 2), ("gb_s" if bytes_ else "tflop_s"): round(rate, 1),
+                     "of_peak": round(rate / (peaks["hbm_gbs"] if bytes_ else peaks["bf16_tflops"]), 4)})
+
+    # ---- the recurrence: single tokens (state in and out) and a prompt
+    for batch in (8, 64):
+        c = 3
+        state = [torch.zeros(batch, nh, dk, dv, device=dev) for _ in range(c)]
+        q, k, v, pre = rnd(batch, nh * dk), rnd(batch, nh * dk, scale=0.1), rnd(batch, nh * dv), rnd(batch, nh * dk)
+        o = torch.empty(batch, nh * dv, device=dev)
+        q_start, slots = torch.arange(batch + 1, dtype=torch.int32, device=dev), torch.arange(batch, dtype=torch.int32, device=dev)
+        bias = torch.zeros(nh * dk, device=dev)
+        add(f"recurrence (decay per channel), decode, batch {batch}", "Qwen2 decode attention below (bytes of the state against bytes of the keys)",
+            lambda i: ops.decayed_state_scan(q, k, v, state[i % c], o, q_start, slots, batch, num_heads=nh, decay_pre=pre, decay_bias=bias,
+                                             tau=16.0, q_scale=0.125), c, bytes_=batch * nh * dk * dv * 8)
+    t = RETODRA_PROMPT
+    state = torch.zeros(1, nh, dk, dv, device=dev)
+    q, k, v, pre = rnd(t, nh * dk), rnd(t, nh * dk, scale=0.1), rnd(t, nh * dv), rnd(t, nh * dk)
+    o = torch.empty(t, nh * dv, device=dev)
+    q_start, slots = torch.tensor([0, t], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    bias, lam = torch.zeros(nh * dk, device=dev), torch.full((nh,), 0.98, device=dev)
+    add(f"recurrence (decay per channel), prompt of {t}", "Qwen2 prefill attention below (float FMA against tensor cores)",
+        lambda i: ops.decayed_state_scan(q, k, v, state, o, q_start, slots, 1, num_heads=nh, decay_pre=pre, decay_bias=bias, tau=16.0, q_scale=0.125),
+        2, flops=4.0 * t * nh * dk * dv)
+    add(f"recurrence (decay per head), prompt of {t}", "",
+        lambda i: ops.decayed_state_scan(q, k, v, state, o, q_start, slots, 1, num_heads=nh, decay_const=lam, silu_inputs=True), 2,
+        flops=4.0 * t * nh * dk * dv)
+    # ---- rows of the residual stream
+    for t in (64, 2048):
+        c = 6 if t == 64 else 3
+        x = [rnd(t, h, dtype=torch.float32) for _ in range(c)]
+        y, o1 = ([rnd(t, h) for _ in range(c)] for _ in range(2))
+        gain = torch.ones(h, device=dev)
+        add(f"post norm + layer scale + addition + next norm, {t} tokens", "", lambda i: ops.norm_residual_norm(y[i % c], gain, x[i % c], 1e-6, next_gain=gain,
+                                                                                                             next_out=o1[i % c], next_eps=1e-6), c, bytes_=t * h * 12)
+        add(f"Qwen2: residual add + RMSNorm, {t} tokens", "like the one above", lambda i: ops.add_rmsnorm(x[i % c], y[i % c], gain, o1[i % c], 1e-6), c, bytes_=t * h * 12)
+        of = [rnd(t, nh * dv, dtype=torch.float32) for _ in range(c)]
+        gt, gw = rnd(t, nh * dv), torch.ones(dv, device=dev)
+        add(f"norm per head + silu gate, {t} tokens", "like the one above", lambda i: ops.gated_group_norm(of[i % c], gt, gw, o1[i % c][:, : nh * dv], group=dv, eps=1e-6,
+                                                                                                        gate_act="silu"), c, bytes_=t * nh * dv * 8)
+        width = (nh + 2 * nkv) * d
+        proj = [rnd(t, width) for _ in range(c)]
+        n_pages = t // page + 2
+        kvc = torch.zeros(n_pages, 2 * nkv * page * d, dtype=bf, device=dev)
+        bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        req, pos = torch.zeros(t, dtype=torch.int32, device=dev), torch.arange(t, dtype=torch.int32, device=dev)
+        wq, wk, q_out = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev), torch.empty(t, nh * d, dtype=bf, device=dev)
+        add(f"q/k norm over the projection + cache write, {t} tokens", "", lambda i: ops.qk_norm_cache_write(
+            proj[i % c], 0, nh * d, (nh + nkv) * d, wq, wk, q_out, kvc, pos, req, bt, num_heads=nh, num_kv_heads=nkv, head_dim=d, v_head_dim=d, row=d,
+            page_size=page, eps=1e-6, write_kv=True), c, bytes_=t * width * 2 + t * (nh + 2 * nkv) * d * 2)
+        denom = torch.from_numpy(np.power(np.float32(1e6), np.arange(d // 2, dtype=np.float32) * 2 / d).astype(np.float32)).to(dev)
+        qb, kv4 = torch.zeros(width, device=dev), kvc.view(n_pages, 2, nkv, page * d)
+        add(f"Qwen2: q/k/v bias + rotation + cache write, {t} tokens", "like the one above", lambda i: ops.rope_cache_write(
+            proj[i % c], qb, pos, req, bt, denom, q_out, kv4, num_heads=nh, num_kv_heads=nkv, head_dim=d, rotary_dim=d, pairing=0, page_size=page,
+            write_kv=True), c, bytes_=t * width * 4)
+    # ---- attention with shaped scores beside plain scores: a prompt, then single tokens
+    t = RETODRA_PROMPT
+    n_pages = t // page + 2
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+    q_start, ctx = torch.tensor([0, t], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    G = nh // nkv
+    n_tiles = -(-t * G // ops.TC_ATTENTION_TILE_ROWS)
+    tile_req = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
+    tile_row0 = torch.from_numpy((np.arange(n_tiles, dtype=np.int32) * ops.TC_ATTENTION_TILE_ROWS)[::-1].copy()).to(dev)
+    q, o = rnd(t, nh * d), torch.empty(t, nh * d, dtype=bf, device=dev)
+    kv = rnd(n_pages, 2, nkv, page * d, scale=0.5)
+    bias_t = rnd(nh, W, dtype=torch.float32)
+    seen = sum(min(i + 1, W) for i in range(t))
+    for shaped, name, like in ((True, f"attention, capped and biased scores, window {W}, prompt of {t}", ""),
+                               (False, f"Qwen2: attention, window {W}, prompt of {t}", "like the one above")):
+        kw = dict(cap=30.0, bias_t=bias_t) if shaped else {}
+        add(name, like, lambda i: ops.attention_prefill_tc(q, kv, o, q_start, ctx, bt, tile_req, tile_row0, num_heads=nh, num_kv_heads=nkv, head_dim=d,
+                                                           page_size=page, window=W, scale=d ** -0.5, **kw), 4, flops=4.0 * nh * d * seen)
+    part = PagedAttention(h, nh, nkv, d, True, False, W, PartSpec("none"), bf, dev)
+    for batch in (8, 64):
+        contexts = [RETODRA_CONTEXT - 1] * batch
+        blocks = -(-RETODRA_CONTEXT // page)
+        bt = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
+        q_start, ctx = torch.arange(batch + 1, dtype=torch.int32, device=dev), torch.tensor(contexts, dtype=torch.int32, device=dev)
+        host = HostStep([1] * batch, contexts, page)
+        split_tiles = torch.from_numpy(part.step_arrays()[part._splits_key()](host)).to(dev)
+        nsplit = host.shapes[part._splits_key()]
+        need = batch * nh * nsplit
+        share = ops.decode_head_groups(nh, nkv)
+        po, pml, tickets = torch.empty(need * d, device=dev), torch.empty(need * 2, device=dev), torch.zeros(batch * nkv * share, dtype=torch.int32, device=dev)
+        q, o = rnd(batch, nh * d), torch.empty(batch, nh * d, dtype=bf, device=dev)
+        kv = rnd(batch * blocks + 1, 2, nkv, page * d, scale=0.5)
+        for shaped, name, like in ((True, f"attention, capped and biased scores, decode, batch {batch}, window {W}", ""),
+                                   (False, f"Qwen2: attention, decode, batch {batch}, window {W}", "like the one above")):
+            kw = dict(cap=30.0, bias_t=bias_t) if shaped else {}
+            add(name, like, lambda i: ops.attention_decode_mma(q, kv, o, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh,
+                                                               num_kv_heads=nkv * share, head_dim=d, page_size=page, window=W, scale=d ** -0.5,
+                                                               split_tiles=split_tiles, kv_share=share, **kw), 4, bytes_=batch * W * 2 * nkv * d * 2)
+    # ---- routed experts beside a dense gated feed-forward of the width the chosen experts have together
+    from vllm_cpp_b200.parts.base import Workspace
+    from vllm_cpp_b200.parts.mlp import GatedMLP
+    from vllm_cpp_b200.parts.moe import RoutedExperts
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    moe = RoutedExperts(h, ff, E, 1, top, 7.0, bf, dev)
+    tensors = {"router": rnd(E + 1, h, dtype=torch.float32, scale=0.05), "correction": torch.zeros(E + 1, device=dev)}
+    for e in range(E):
+        tensors.update({f"e{e}.gate": rnd(ff, h, scale=0.02), f"e{e}.up": rnd(ff, h, scale=0.02), f"e{e}.down": rnd(h, ff, scale=0.02)})
+    moe.load_params(tensors)
+    del tensors
+    dense = [GatedMLP(h, top * ff, "silu", bf, dev) for _ in range(3)]
+    for m in dense:
+        m.load_params({"gate_proj.weight": rnd(top * ff, h, scale=0.02), "up_proj.weight": rnd(top * ff, h, scale=0.02),
+                       "down_proj.weight": rnd(h, top * ff, scale=0.02)})
+        ops.tile_weights(m.w_gate_up, top * ff)
+        ops.tile_weights(m.w_down)
+    ws = Workspace(dev, 1 << 30)
+    for t in (8, 64, 2048):
+        x, out = rnd(t, h), torch.empty(t, h, dtype=bf, device=dev)
+
+        def run_moe(i):
+            ws.reset()
+            moe.forward(x, out, None, ws)
+
+        def run_dense(i):
+            ws.reset()
+            dense[i % 3].forward(x, out, None, ws)
+
+        reach = min(E, t * top)
+        if t <= 128:
+            add(f"routed experts ({top} of {E}, five kernels), {t} tokens", "", run_moe, 3, bytes_=reach * 3 * ff * h * 2)
+            add(f"Qwen2: gated feed-forward of width {top * ff}, {t} tokens", "like the one above", run_dense, 3, bytes_=3 * top * ff * h * 2)
+        else:
+            add(f"routed experts ({top} of {E}, five kernels), {t} tokens", "", run_moe, 3, flops=6.0 * t * top * ff * h)
+            add(f"Qwen2: gated feed-forward of width {top * ff}, {t} tokens", "like the one above", run_dense, 3, flops=6.0 * t * top * ff * h)
+    ops.check_status()
+    return rows
+
+
 # ------------------------------------------------------------------------------------------ reference arm
 REFERENCE_NOTES = ("the reference's own faults at these sizes, none of which changes the work of a step: an untied lm_head is "
                    "copied over the embedding table (src/model/qwen.cpp:279-281); the bias area of 3*1024 floats a layer "
@@ -809,6 +1128,10 @@ def main() -> int:
                     help="instead of the benchmark's workload: prefill and decode throughput of the Rolesun design beside Qwen2 "
                          f"at equal layer sizes ({','.join(sorted(ROLESUN_SIZES))} or 'all'), and the design's kernels alone "
                          "beside the like kernels of Qwen2's layer")
+    ap.add_argument("--retodra", default="", metavar="SIZES",
+                    help="instead of the benchmark's workload: prefill and decode throughput of the Retodra design beside Qwen2 "
+                         f"at equal layer sizes ({','.join(sorted(RETODRA_SIZES))} or 'all'), and the design's kernels alone "
+                         "beside the like kernels of Qwen2's layer")
     a = ap.parse_args()
     if a.contexts:
         CONTEXT_START, CONTEXT = (int(v) for v in a.contexts.split(","))
@@ -842,6 +1165,8 @@ def main() -> int:
         ops.set_tcgen05_linear(False)
     if a.rolesun:
         return run_rolesun(a)
+    if a.retodra:
+        return run_retodra(a)
     if a.mix:
         return run_mix(cfg, a)
     if a.kernels:

@@ -157,6 +157,58 @@ def test_recurrence_under_every_cut_with_slots_used_again(dtype, H, dk, dv, kind
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,dk,dv,kind", [(2, 48, 64, "channel"), (3, 16, 24, "head"), (1, 72, 130, "channel")])
+def test_recurrence_in_pieces_side_by_side(dtype, H, dk, dv, kind):
+    """Long portions cut into pieces that run side by side and are joined: the same outputs and the same final state
+    as token by token, for a long request beside a short one, over two steps."""
+    from vllm_cpp_b200.csrc import ops
+    rng = np.random.default_rng(dk + dv)
+    tau, scale = 2.0, 0.5
+    lengths = {"a": 415, "b": 131}
+    bias = rng.standard_normal(H * dk).astype(np.float32) + 3
+    lam = rng.uniform(0.9, 1.0, H).astype(np.float32)
+    data, want, final = {}, {}, {}
+    for r, n in lengths.items():
+        q, k = stored(rng.standard_normal((n, H * dk)), dtype), stored(rng.standard_normal((n, H * dk)) / np.sqrt(dk), dtype)
+        v, pre = stored(rng.standard_normal((n, H * dv)), dtype), stored(2 * rng.standard_normal((n, H * dk)), dtype)
+        data[r] = (q, k, v, pre)
+        outs, ends = [], []
+        for h in range(H):
+            sl, vs = slice(h * dk, (h + 1) * dk), slice(h * dv, (h + 1) * dv)
+            if kind == "channel":
+                o, S = plain.decayed_outer_recurrence(q[:, sl] * scale, k[:, sl], v[:, vs], plain.sigmoid(pre[:, sl] + bias[sl]) ** (1 / tau))
+            else:
+                o, S = plain.decayed_outer_recurrence(plain.silu(q[:, sl]), plain.silu(k[:, sl]), plain.silu(v[:, vs]), np.full((n, dk), float(lam[h])))
+            outs.append(o)
+            ends.append(S)
+        want[r], final[r] = np.concatenate(outs, axis=1), np.stack(ends)
+    state = torch.zeros((2, H, dk, dv), device="cuda")
+    slot, at, got = {"a": 1, "b": 0}, {"a": 0, "b": 0}, {"a": [], "b": []}
+    for step in ([("a", 300), ("b", 1)], [("b", 130), ("a", 115)]):
+        rows = [dev(np.concatenate([data[r][i][at[r]: at[r] + n] for r, n in step]), DT[dtype]) for i in range(4)]
+        n_rows = rows[0].shape[0]
+        starts, per_req = ops.scan_pieces([n for _, n in step])
+        count = len(starts) - 1
+        pieces = {"start": dev(starts), "req": dev(per_req), "slots": dev(np.arange(count, dtype=np.int32)), "count": count,
+                  "state": torch.full((count, H, dk, dv), 7.0, device="cuda"), "qp": torch.empty((n_rows, H * dk), device="cuda"),
+                  "dtot": torch.empty((count, H * dk), device="cuda")}
+        q_start = dev(np.cumsum([0] + [n for _, n in step]).astype(np.int32))
+        slots = dev(np.array([slot[r] for r, _ in step], dtype=np.int32))
+        out = torch.empty((n_rows, H * dv), dtype=torch.float32, device="cuda")
+        kw = dict(decay_pre=rows[3], decay_bias=dev(bias), tau=tau, q_scale=scale) if kind == "channel" else dict(decay_const=dev(lam), silu_inputs=True)
+        ops.decayed_state_scan(rows[0], rows[1], rows[2], state, out, q_start, slots, len(step), num_heads=H, pieces=pieces, **kw)
+        o, t0 = out.cpu().numpy(), 0
+        for r, n in step:
+            got[r].append(o[t0: t0 + n])
+            t0 += n
+            at[r] += n
+    for r in lengths:
+        g = np.concatenate(got[r])
+        assert np.abs(g - want[r]).max() <= 3e-5 * np.abs(want[r]).max(), (r, np.abs(g - want[r]).max(), np.abs(want[r]).max())
+        assert np.abs(state[slot[r]].cpu().numpy() - final[r]).max() <= 3e-5 * np.abs(final[r]).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,dv,whole,act", [(3, 24, False, "silu"), (5, 40, True, "sigmoid"), (1, 72, False, "sigmoid"), (2, 320, True, "silu")])
 def test_group_norm_with_gate(dtype, heads, dv, whole, act):
     from vllm_cpp_b200.csrc import ops

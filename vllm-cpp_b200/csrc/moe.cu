@@ -222,6 +222,126 @@ moe_expert_gemm_kernel(const T* __restrict__ A, long long lda, const T* __restri
     }
 }
 
+// The same products for bfloat16 on the tensor cores (mma.sync m16n8k16, float accumulators): a CTA of four warps
+// owns TM rows x 64 columns of a tile (and, gated, the 64 up columns beside the 64 gate columns); a ring of three
+// 32-deep k slices is filled with cp.async (16-byte pieces; rows beyond the tile and k beyond K arrive as zeros),
+// fragments come out of shared memory with ldmatrix (rows padded to 80 bytes: no bank conflicts).  K and the rows'
+// strides must be multiples of 8 elements.
+#define MM_BN 64
+#define MM_BK 32
+#define MM_LDS (MM_BK + 8)
+#define MM_STAGES 3
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int TM, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W, void* __restrict__ Cv,
+                      long long ldc, int N, int K, const int* __restrict__ sorted_token, const int* __restrict__ tile_expert,
+                      const int* __restrict__ tile_row0, const int* __restrict__ tile_rows, const int* __restrict__ meta,
+                      float limit, float alpha) {
+    constexpr int WR = GATED ? 2 * MM_BN : MM_BN, MF = TM / 16;
+    __shared__ __align__(16) __nv_bfloat16 As[MM_STAGES][TM][MM_LDS];
+    __shared__ __align__(16) __nv_bfloat16 Ws[MM_STAGES][WR][MM_LDS];
+    __shared__ int src[TM];
+    pdl_start();
+    const int tile = blockIdx.y;
+    if (tile >= meta[0]) return;
+    const int e = tile_expert[tile], r0 = tile_row0[tile], rows = tile_rows[tile];
+    const int n0 = blockIdx.x * MM_BN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < TM) src[tid] = tid < rows ? (GATED ? sorted_token[r0 + tid] : r0 + tid) : -1;
+    __syncthreads();
+    const __nv_bfloat16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    const int KT = (K + MM_BK - 1) / MM_BK;
+
+    auto load_stage = [&](int kt, int buf) {
+        const int k0 = kt * MM_BK;
+        for (int idx = tid; idx < TM * 4; idx += 128) {
+            const int r = idx >> 2, k = k0 + (idx & 3) * 8;
+            const bool ok = src[r] >= 0 && k < K;
+            cp_async_16(&As[buf][r][(idx & 3) * 8], ok ? A + (size_t)src[r] * lda + k : A, ok);
+        }
+        for (int idx = tid; idx < WR * 4; idx += 128) {
+            const int r = idx >> 2, k = k0 + (idx & 3) * 8;
+            const int n = n0 + (r % MM_BN);
+            const bool ok = n < N && k < K;
+            const size_t wrow = (size_t)(GATED && r >= MM_BN ? N + n : n);
+            cp_async_16(&Ws[buf][r][(idx & 3) * 8], ok ? We + wrow * K + k : We, ok);
+        }
+    };
+
+    float acc[MF][2][4], accu[GATED ? MF : 1][2][4];
+#pragma unroll
+    for (int i = 0; i < MF; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { acc[i][j][c] = 0.0f; if (GATED) accu[i][j][c] = 0.0f; }
+
+#pragma unroll
+    for (int st = 0; st < MM_STAGES - 1; ++st) {
+        if (st < KT) load_stage(st, st);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(MM_STAGES - 2) : "memory");
+        __syncthreads();                                  // slice kt has landed for everyone; the slice before has been read
+        if (kt + MM_STAGES - 1 < KT) load_stage(kt + MM_STAGES - 1, (kt + MM_STAGES - 1) % MM_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int buf = kt % MM_STAGES;
+#pragma unroll
+        for (int ks = 0; ks < MM_BK; ks += 16) {
+            uint32_t b[4], bu[4];
+            ldmatrix_x4(b, &Ws[buf][warp * 16 + (lane & 7) + (lane >> 4) * 8][ks + ((lane >> 3) & 1) * 8]);
+            if (GATED) ldmatrix_x4(bu, &Ws[buf][MM_BN + warp * 16 + (lane & 7) + (lane >> 4) * 8][ks + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+            for (int mi = 0; mi < MF; ++mi) {
+                uint32_t a[4];
+                ldmatrix_x4(a, &As[buf][mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][ks + (lane >> 4) * 8]);
+                mma_bf16(acc[mi][0], a, b[0], b[1]);
+                mma_bf16(acc[mi][1], a, b[2], b[3]);
+                if (GATED) {
+                    mma_bf16(accu[mi][0], a, bu[0], bu[1]);
+                    mma_bf16(accu[mi][1], a, bu[2], bu[3]);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int mi = 0; mi < MF; ++mi)
+#pragma unroll
+        for (int nf = 0; nf < 2; ++nf)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int m = mi * 16 + (lane >> 2) + (c >> 1) * 8;
+                const int n = n0 + warp * 16 + nf * 8 + (lane & 3) * 2 + (c & 1);
+                if (m >= rows || n >= N) continue;
+                if (GATED) {
+                    const float g = fminf(acc[mi][nf][c], limit);
+                    const float u = fminf(fmaxf(accu[mi][nf][c], -limit), limit);
+                    const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+                    ((__nv_bfloat16*)Cv)[(size_t)(r0 + m) * ldc + n] = __float2bfloat16_rn(y);
+                } else {
+                    ((float*)Cv)[(size_t)(r0 + m) * ldc + n] = acc[mi][nf][c];
+                }
+            }
+}
+
 // gated 1: A = the tokens' rows [n, K] (T), W [E, 2 * N, K], C [pairs, N] (T).  gated 0: A [pairs, K] (T), W [E, N, K],
 // C [pairs, N] float.  max_tiles: the grid's height; tm: 16 or 64, the tile height moe_sort was given.
 VCB_EXPORT int vcb_moe_expert_gemm(const void* A, long long lda, const void* W, void* C, long long ldc, int N, int K,
@@ -232,6 +352,15 @@ VCB_EXPORT int vcb_moe_expert_gemm(const void* A, long long lda, const void* W, 
     if (!A || !W || !C || N <= 0 || K <= 0 || (tm != 16 && tm != 64) || max_tiles > 65535) return VCB_ERR_BAD_ARG;
     dim3 grid((N + MG_N - 1) / MG_N, max_tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_BF16 && K % 8 == 0 && lda % 8 == 0 && !(((uintptr_t)A | (uintptr_t)W) & 15)) {
+        // the tensor-core form
+#define MOE_MMA(TMV, G) vcb_launch(moe_expert_mma_kernel<TMV, G>, grid, 128, 0, s, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, C, ldc, N, K, \
+                                   sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha)
+        if (tm == 16) { if (gated) MOE_MMA(16, true); else MOE_MMA(16, false); }
+        else { if (gated) MOE_MMA(64, true); else MOE_MMA(64, false); }
+#undef MOE_MMA
+        return vcb_last_error();
+    }
 #define MOE_GO(TT, TMV, G) vcb_launch(moe_expert_gemm_kernel<TT, TMV, G>, grid, 256, 0, s, (const TT*)A, lda, (const TT*)W, C, ldc, N, K, \
                                       sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha)
     if (dtype == VCB_F32) {

@@ -58,7 +58,8 @@ _SIGNATURES = {
     "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P],
     "vcb_embedding_scaled": [_P, _P, _P, _I, _I, _I, _P, _F, _I, _P],
     "vcb_norm_residual_norm": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P],
-    "vcb_decayed_state_scan": [_P, _P, _P, _P, _L, _L, _L, _L, _P, _P, _F, _F, _I, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_decayed_state_scan": [_P, _P, _P, _P, _L, _L, _L, _L, _P, _P, _F, _F, _I, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P, _L, _P, _I, _P],
+    "vcb_decayed_state_join": [_P, _L, _P, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "vcb_gated_group_norm": [_P, _L, _P, _L, _P, _I, _P, _L, _I, _I, _I, _I, _F, _I, _P],
     "vcb_scaled_sum": [_P, _P, _P, _L, _F, _F, _I, _P],
     "vcb_qk_norm_cache_write": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
@@ -880,13 +881,18 @@ def decayed_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state:
                        q_start: torch.Tensor, state_slots: torch.Tensor, n_reqs: int, *, num_heads: int,
                        decay_pre: Optional[torch.Tensor] = None, decay_bias: Optional[torch.Tensor] = None,
                        decay_const: Optional[torch.Tensor] = None, tau: float = 1.0, q_scale: float = 1.0,
-                       silu_inputs: bool = False) -> None:
+                       silu_inputs: bool = False, pieces: Optional[dict] = None) -> None:
     """Per request and head, over the step's tokens:  S = diag(a_t) S + k_t v_t^T;  out_t = S^T q_t, with S (float32
     [dk, dv]) read from and left in the request's slot of ``state`` [slots, heads, dk, dv].  q, k [n, heads * dk] and
     v [n, heads * dv] are rows (strided views allowed) of the activations' type; out float32 [n, heads * dv].  The decay:
     ``decay_pre`` ([n, heads * dk]) gives a_t = sigmoid(decay_pre + decay_bias)^(1 / tau) per key channel;
     ``decay_const`` (float32 [heads]) one number per head; neither: 1.  ``silu_inputs``: q, k and v pass through
-    silu; ``q_scale`` multiplies q."""
+    silu; ``q_scale`` multiplies q.
+
+    ``pieces`` (for steps with long portions): the portions cut into pieces of at most SCAN_PIECE tokens that run side
+    by side, then are joined (csrc/recurrent.cu): {"start": int32 [pieces + 1] first rows, "req": int32 [n_reqs + 1] the
+    pieces of each request, "slots": int32 [pieces] = 0 .. pieces - 1, "count": pieces, "state": float32 scratch
+    [pieces, heads, dk, dv], "qp": float32 scratch [n, heads * dk], "dtot": float32 scratch [pieces, heads, dk]}."""
     n = q.shape[0]
     H = num_heads
     _need(q.shape[1] % H == 0 and v.shape[1] % H == 0, "decayed_state_scan: widths must be multiples of the head count")
@@ -904,6 +910,27 @@ def decayed_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state:
         _need(decay_bias is None or decay_bias.numel() == H * dk, "decayed_state_scan: decay_bias [heads * dk]")
     if decay_const is not None:
         _need(decay_const.numel() == H, "decayed_state_scan: decay_const [heads]")
+    if pieces is not None:
+        count = int(pieces["count"])
+        ps, qp, dtot = pieces["state"], pieces["qp"], pieces["dtot"]
+        _need(ps.dtype == torch.float32 and ps.is_contiguous() and tuple(ps.shape) == (count, H, dk, dv)
+              and qp.dtype == torch.float32 and qp.is_contiguous() and tuple(qp.shape) == (n, H * dk)
+              and dtot.dtype == torch.float32 and dtot.is_contiguous() and dtot.numel() == count * H * dk,
+              "decayed_state_scan: scratch of the pieces")
+        _check(lib().vcb_decayed_state_scan(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), None if decay_pre is None else decay_pre.data_ptr(),
+            q.stride(0), k.stride(0), v.stride(0), 0 if decay_pre is None else decay_pre.stride(0),
+            None if decay_bias is None else _dev(decay_bias, "decay_bias", torch.float32),
+            None if decay_const is None else _dev(decay_const, "decay_const", torch.float32),
+            1.0 / float(tau), float(q_scale), 1 if silu_inputs else 0, ps.data_ptr(), out.data_ptr(), out.stride(0),
+            _dev(pieces["start"], "pieces.start", torch.int32), _dev(pieces["slots"], "pieces.slots", torch.int32), count, H, dk, dv,
+            1, qp.data_ptr(), qp.stride(0), dtot.data_ptr(), dtype_code(q.dtype), _stream()), "decayed_state_scan")
+        _check(lib().vcb_decayed_state_join(qp.data_ptr(), qp.stride(0), ps.data_ptr(), dtot.data_ptr(), state.data_ptr(),
+                                            out.data_ptr(), out.stride(0), pieces["start"].data_ptr(),
+                                            _dev(pieces["req"], "pieces.req", torch.int32), _dev(state_slots, "state_slots", torch.int32),
+                                            count, n_reqs, H, dk, dv, _stream()), "decayed_state_join")
+        add_launches(1)            # the join is two kernels
+        return
     _check(lib().vcb_decayed_state_scan(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), None if decay_pre is None else decay_pre.data_ptr(),
         q.stride(0), k.stride(0), v.stride(0), 0 if decay_pre is None else decay_pre.stride(0),
@@ -911,7 +938,26 @@ def decayed_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state:
         None if decay_const is None else _dev(decay_const, "decay_const", torch.float32),
         1.0 / float(tau), float(q_scale), 1 if silu_inputs else 0, state.data_ptr(), out.data_ptr(), out.stride(0),
         _dev(q_start, "q_start", torch.int32), _dev(state_slots, "state_slots", torch.int32), n_reqs, H, dk, dv,
-        dtype_code(q.dtype), _stream()), "decayed_state_scan")
+        0, None, 0, None, dtype_code(q.dtype), _stream()), "decayed_state_scan")
+
+
+SCAN_PIECE = 128          # tokens of a piece of a long portion (decayed_state_scan with ``pieces``)
+
+
+def scan_pieces(q_lens):
+    """Cuts a step's portions into pieces of at most SCAN_PIECE tokens: (first rows [pieces + 1], pieces of each request
+    [n_reqs + 1]) as int32 arrays."""
+    import numpy as np
+    starts, per_req, row = [0], [0], 0
+    for n in q_lens:
+        left = int(n)
+        while left > 0:
+            take = min(SCAN_PIECE, left)
+            row += take
+            left -= take
+            starts.append(row)
+        per_req.append(len(starts) - 1)
+    return np.asarray(starts, dtype=np.int32), np.asarray(per_req, dtype=np.int32)
 
 
 def gated_group_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor, *, group: int,

@@ -32,6 +32,14 @@ struct ScanArgs {
     const int* q_start;
     const int* state_slots;
     int H, dk, dv, chunk;       // chunk: tokens staged in shared memory at a time
+    // For long portions cut into pieces that run side by side (see decayed_state_carry_kernel): every piece is a
+    // "request" of its own here.  fresh: S starts from zero and the slot is only written.  qp (may be null): float
+    // [n, H * dk], row stride ldqp, receives q_t (activated, scaled) times the product of the decays from the piece's
+    // first token through t; dtot (may be null): float [pieces, H, dk], the product over the whole piece.
+    int fresh;
+    float* qp;
+    long long ldqp;
+    float* dtot;
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -53,6 +61,7 @@ __global__ void decayed_state_scan_kernel(ScanArgs a) {
     float* as = ks + TC * dkpad;
     float* vs = as + TC * dkpad;
     float* ps = vs + TC * dvt;
+    float* carry = ps + parts * TC * dvt;         // [dkpad]: product of the decays so far, per key channel
     const int row0 = a.q_start[r], row1 = a.q_start[r + 1];
     const int col = col0 + tx;
     const bool col_ok = col < a.dv;
@@ -61,9 +70,11 @@ __global__ void decayed_state_scan_kernel(ScanArgs a) {
 #pragma unroll
     for (int i = 0; i < DKP; ++i) {
         const int kr = part * DKP + i;
-        S[i] = (col_ok && kr < a.dk) ? st[(size_t)kr * a.dv + col] : 0.0f;
+        S[i] = (col_ok && kr < a.dk && !a.fresh) ? st[(size_t)kr * a.dv + col] : 0.0f;
     }
     const int tid = part * dvt + tx, nthreads = dvt * parts;
+    const bool tracks = (a.qp || a.dtot) && blockIdx.z == 0;      // one block per (piece, head) follows the decays' product
+    if (tracks) for (int i = tid; i < dkpad; i += nthreads) carry[i] = 1.0f;
     const float dconst = a.decay_const ? a.decay_const[h] : 1.0f;
     const T* q = (const T*)a.q;
     const T* k = (const T*)a.k;
@@ -100,6 +111,16 @@ __global__ void decayed_state_scan_kernel(ScanArgs a) {
             vs[idx] = vv;
         }
         __syncthreads();
+        if (tracks) {
+            for (int i = tid; i < a.dk; i += nthreads) {
+                float run = carry[i];
+                for (int tt = 0; tt < tc; ++tt) {
+                    run *= as[tt * dkpad + i];
+                    if (a.qp) a.qp[(size_t)(c0 + tt) * a.ldqp + h * a.dk + i] = qs[tt * dkpad + i] * run;
+                }
+                carry[i] = run;
+            }
+        }
         for (int tt = 0; tt < tc; ++tt) {
             const float vv = vs[tt * dvt + tx];
             const float* qq = qs + tt * dkpad + part * DKP;
@@ -127,6 +148,10 @@ __global__ void decayed_state_scan_kernel(ScanArgs a) {
         const int kr = part * DKP + i;
         if (col_ok && kr < a.dk) st[(size_t)kr * a.dv + col] = S[i];
     }
+    if (tracks && a.dtot) {
+        __syncthreads();
+        for (int i = tid; i < a.dk; i += nthreads) a.dtot[((size_t)r * a.H + h) * a.dk + i] = carry[i];
+    }
 }
 
 template <typename T>
@@ -140,7 +165,7 @@ static int launch_scan(const ScanArgs& a, int n_reqs, cudaStream_t s) {
     const int dvt = (a.dv <= 32 || wide_blocks < 2LL * vcb_sm_count()) ? 32 : 64;
     const int dkpad = parts * dkp;
     int chunk = 16;
-    auto bytes = [&](int tc) { return (size_t)tc * (3 * dkpad + dvt + parts * dvt) * sizeof(float); };
+    auto bytes = [&](int tc) { return ((size_t)tc * (3 * dkpad + dvt + parts * dvt) + dkpad) * sizeof(float); };
     while (chunk > 1 && bytes(chunk) > 48 * 1024) chunk >>= 1;
     ScanArgs b = a;
     b.chunk = chunk;
@@ -155,16 +180,110 @@ VCB_EXPORT int vcb_decayed_state_scan(const void* q, const void* k, const void* 
                                       long long ldq, long long ldk, long long ldv, long long ldd,
                                       const float* decay_bias, const float* decay_const, float inv_tau, float q_scale,
                                       int act, float* state, float* out, long long ldo, const int* q_start,
-                                      const int* state_slots, int n_reqs, int H, int dk, int dv, int dtype, void* stream) {
+                                      const int* state_slots, int n_reqs, int H, int dk, int dv, int fresh, float* qp,
+                                      long long ldqp, float* dtot, int dtype, void* stream) {
     if (n_reqs <= 0) return 0;
     if (!q || !k || !v || !state || !out || H <= 0 || dk <= 0 || dv <= 0 || H > 65535) return VCB_ERR_BAD_ARG;
     if ((dv + 31) / 32 > 65535) return VCB_ERR_UNSUPPORTED;
     ScanArgs a{q, k, v, decay_pre, ldq, ldk, ldv, ldd, decay_bias, decay_const, inv_tau, q_scale, act, state, out, ldo,
-               q_start, state_slots, H, dk, dv, 0};
+               q_start, state_slots, H, dk, dv, 0, fresh, qp, ldqp, dtot};
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VCB_F32) return launch_scan<float>(a, n_reqs, s);
     if (dtype == VCB_BF16) return launch_scan<__nv_bfloat16>(a, n_reqs, s);
     return VCB_ERR_BAD_ARG;
+}
+
+// ------------------------------------------------------------- long portions: pieces side by side
+// A long portion is cut into pieces.  decayed_state_scan_kernel runs every piece as if it were a request that starts from
+// a zero state: its outputs are then right but for what the state before the piece adds, and its end state is the
+// piece's own contribution.  With P_t the product of the decays from the piece's first token through t:
+//     S_before(next piece) = diag(P_last) S_before(piece) + S_end(piece)            (decayed_state_carry_kernel)
+//     o_t += (q_t * P_t)^T S_before(piece)                                          (decayed_state_inter_kernel)
+// Every factor is a product of decays (at most 1): nothing is ever divided by a decay.
+//
+// One thread per element of S: walks the pieces of its request in order, leaves in piece_state the state before each
+// piece and in the request's slot the state after the last.
+__global__ void decayed_state_carry_kernel(float* __restrict__ piece_state, const float* __restrict__ dtot, float* __restrict__ state,
+                                           const int* __restrict__ req_pieces, const int* __restrict__ state_slots, int H, int dk, int dv) {
+    pdl_start();
+    const int r = blockIdx.y;
+    const size_t per = (size_t)H * dk * dv;
+    const int p0 = req_pieces[r], p1 = req_pieces[r + 1];
+    float* slot = state + (size_t)state_slots[r] * per;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < per; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t hi = e / dv;                     // (head, key channel)
+        float S = slot[e];
+        for (int p = p0; p < p1; ++p) {
+            const float own = piece_state[(size_t)p * per + e];
+            piece_state[(size_t)p * per + e] = S;
+            S = fmaf(dtot[(size_t)p * H * dk + hi], S, own);
+        }
+        slot[e] = S;
+    }
+}
+
+// Grid (piece, head, tile of 64 value channels), block (64, 4): thread (x, y) owns column x for the piece's tokens
+// y, y + 4, ...; key channels pass through shared memory in slabs of 32.
+#define INTER_MAX_TOKENS 128
+__global__ void __launch_bounds__(256)
+decayed_state_inter_kernel(const float* __restrict__ qp, long long ldqp, const float* __restrict__ piece_state, float* __restrict__ out,
+                           long long ldo, const int* __restrict__ piece_start, int H, int dk, int dv) {
+    __shared__ float qs[INTER_MAX_TOKENS][33];
+    __shared__ float ss[32][64];
+    pdl_start();
+    const int p = blockIdx.x, h = blockIdx.y, col = blockIdx.z * 64 + threadIdx.x;
+    const int row0 = piece_start[p], rows = min(piece_start[p + 1] - row0, INTER_MAX_TOKENS);
+    const float* S = piece_state + (((size_t)p * H + h) * dk) * dv;
+    const int tid = threadIdx.y * 64 + threadIdx.x;
+    float acc[INTER_MAX_TOKENS / 4];
+#pragma unroll
+    for (int i = 0; i < INTER_MAX_TOKENS / 4; ++i) acc[i] = 0.0f;
+    for (int i0 = 0; i0 < dk; i0 += 32) {
+        __syncthreads();
+        for (int idx = tid; idx < rows * 32; idx += 256) {
+            const int t = idx >> 5, i = idx & 31;
+            qs[t][i] = i0 + i < dk ? qp[(size_t)(row0 + t) * ldqp + h * dk + i0 + i] : 0.0f;
+        }
+        for (int idx = tid; idx < 32 * 64; idx += 256) {
+            const int i = idx >> 6, c = blockIdx.z * 64 + (idx & 63);
+            ss[i][idx & 63] = (i0 + i < dk && c < dv) ? S[(size_t)(i0 + i) * dv + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < INTER_MAX_TOKENS / 4; ++k) {
+            const int t = threadIdx.y + 4 * k;
+            if (t < rows) {
+                float s = acc[k];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s = fmaf(qs[t][i], ss[i][threadIdx.x], s);
+                acc[k] = s;
+            }
+        }
+    }
+    if (col < dv) {
+#pragma unroll
+        for (int k = 0; k < INTER_MAX_TOKENS / 4; ++k) {
+            const int t = threadIdx.y + 4 * k;
+            if (t < rows) out[(size_t)(row0 + t) * ldo + h * dv + col] += acc[k];
+        }
+    }
+}
+
+// piece_state: [pieces, H, dk, dv] as decayed_state_scan left it (fresh, slots 0 .. pieces - 1); req_pieces [n_reqs + 1]:
+// the pieces of request r are req_pieces[r] .. req_pieces[r + 1] - 1; piece_start [pieces + 1]: their first rows.  No piece
+// is longer than 128 tokens.
+VCB_EXPORT int vcb_decayed_state_join(const float* qp, long long ldqp, float* piece_state, const float* dtot, float* state,
+                                      float* out, long long ldo, const int* piece_start, const int* req_pieces,
+                                      const int* state_slots, int n_pieces, int n_reqs, int H, int dk, int dv, void* stream) {
+    if (n_pieces <= 0 || n_reqs <= 0) return 0;
+    if (!qp || !piece_state || !dtot || !state || !out || H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || n_reqs > 65535) return VCB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t per = (size_t)H * dk * dv;
+    const int blocks = (int)((per + 255) / 256 < 1024 ? (per + 255) / 256 : 1024);
+    vcb_launch(decayed_state_carry_kernel, dim3(blocks, n_reqs), 256, 0, s, piece_state, dtot, state, req_pieces, state_slots, H, dk, dv);
+    vcb_launch(decayed_state_inter_kernel, dim3(n_pieces, H, (dv + 63) / 64), dim3(64, 4), 0, s, qp, ldqp, (const float*)piece_state, out, ldo,
+               piece_start, H, dk, dv);
+    return vcb_last_error();
 }
 
 // ------------------------------------------------------------- norm over groups of channels, times a gate

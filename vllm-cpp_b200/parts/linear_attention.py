@@ -21,6 +21,7 @@ from __future__ import annotations
 
 from typing import Dict, Sequence
 
+import numpy as np
 import torch
 
 from ..csrc import ops
@@ -56,8 +57,36 @@ class DecayedStateMixer(Mixer):
 
     def workspace_bytes(self, n_tokens, n_reqs):
         c = self.heads * self.dv
+        most_pieces = n_tokens // ops.SCAN_PIECE + n_reqs
+        pieces = (workspace_piece((most_pieces, self.heads, self.dk, self.dv), torch.float32)
+                  + workspace_piece((n_tokens, self.heads * self.dk), torch.float32) + workspace_piece((most_pieces, self.heads * self.dk), torch.float32))
         return (workspace_piece((n_tokens, sum(self.in_rows())), self.dtype) + workspace_piece((n_tokens, self.heads * self.dk), self.dtype)
-                + workspace_piece((n_tokens, c), torch.float32) + workspace_piece((n_tokens, c), self.dtype))
+                + workspace_piece((n_tokens, c), torch.float32) + workspace_piece((n_tokens, c), self.dtype)
+                + (pieces if n_tokens > ops.SCAN_PIECE else 0))
+
+    def step_arrays(self):
+        """A step with a portion longer than ops.SCAN_PIECE tokens runs the recurrence in pieces side by side
+        (ops.decayed_state_scan with ``pieces``): the pieces' first rows, the pieces of each request and the scratch
+        slots they use, and their number as a launch shape.  Other steps get placeholders."""
+        def cut(host):
+            if max(host.q_lens) <= ops.SCAN_PIECE:
+                return None
+            starts, per_req = ops.scan_pieces(host.q_lens)
+            host.shapes["scan_pieces"] = len(starts) - 1
+            return starts, per_req
+        none = np.zeros(1, dtype=np.int32)
+        return {"scan_piece_start": lambda host: none if cut(host) is None else cut(host)[0],
+                "scan_piece_req": lambda host: none if cut(host) is None else cut(host)[1],
+                "scan_piece_slots": lambda host: none if cut(host) is None else np.arange(len(cut(host)[0]) - 1, dtype=np.int32)}
+
+    def pieces(self, step, ws):
+        """The ``pieces`` argument of ops.decayed_state_scan for this step (None: the step has no long portion)."""
+        count = step.shapes.get("scan_pieces")
+        if not count or step.max_q_len <= ops.SCAN_PIECE:
+            return None
+        return {"start": step.extras["scan_piece_start"], "req": step.extras["scan_piece_req"], "slots": step.extras["scan_piece_slots"],
+                "count": count, "state": ws.take((count, self.heads, self.dk, self.dv), torch.float32),
+                "qp": ws.take((step.n_tokens, self.heads * self.dk), torch.float32), "dtot": ws.take((count, self.heads * self.dk), torch.float32)}
 
     def product_weights(self):
         return [(self.w_in, 0), (self.w_o, 0)]
@@ -113,7 +142,8 @@ class GatedLinearAttention(DecayedStateMixer):
         ops.linear(low, self.w_a2, pre)
         o = ws.take((n, H * self.dv), torch.float32)
         ops.decayed_state_scan(q, k, v, cache.slots, o, step.q_start, step.state_slots, step.n_reqs, num_heads=H,
-                               decay_pre=pre, decay_bias=self.b_a, tau=self.tau, q_scale=float(self.dk) ** -0.5)
+                               decay_pre=pre, decay_bias=self.b_a, tau=self.tau, q_scale=float(self.dk) ** -0.5,
+                               pieces=self.pieces(step, ws))
         act = ws.take((n, H * self.dv), self.dtype)
         ops.gated_group_norm(o, g, self.w_norm, act, group=self.dv, eps=self.eps, gate_act="silu")
         ops.linear(act, self.w_o, out)
@@ -150,7 +180,7 @@ class LightningAttention(DecayedStateMixer):
         q, k, v, g = self._split(proj)
         o = ws.take((n, H * self.dv), torch.float32)
         ops.decayed_state_scan(q, k, v, cache.slots, o, step.q_start, step.state_slots, step.n_reqs, num_heads=H,
-                               decay_const=self.decay, silu_inputs=True)
+                               decay_const=self.decay, silu_inputs=True, pieces=self.pieces(step, ws))
         act = ws.take((n, H * self.dv), self.dtype)
         ops.gated_group_norm(o, g, self.w_norm, act, group=H * self.dv, eps=self.eps, gate_act="sigmoid")
         ops.linear(act, self.w_o, out)
