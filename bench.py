@@ -865,12 +865,22 @@ def retodra_kernels(z, peaks):
     o = torch.empty(t, nh * dv, device=dev)
     q_start, slots = torch.tensor([0, t], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
     bias, lam = torch.zeros(nh * dk, device=dev), torch.full((nh,), 0.98, device=dev)
-    add(f"recurrence (decay per channel), prompt of {t}", "Qwen2 prefill attention below (float FMA against tensor cores)",
+    starts, per_req = ops.scan_pieces([t])
+    count = len(starts) - 1
+    pieces = {"start": torch.from_numpy(starts).to(dev), "req": torch.from_numpy(per_req).to(dev),
+              "slots": torch.arange(count, dtype=torch.int32, device=dev), "count": count,
+              "state": torch.empty(count, nh, dk, dv, device=dev), "qp": torch.empty(t, nh * dk, device=dev),
+              "dtot": torch.empty(count, nh * dk, device=dev)}
+    add(f"recurrence (decay per channel), prompt of {t}, token by token", "",
         lambda i: ops.decayed_state_scan(q, k, v, state, o, q_start, slots, 1, num_heads=nh, decay_pre=pre, decay_bias=bias, tau=16.0, q_scale=0.125),
         2, flops=4.0 * t * nh * dk * dv)
-    add(f"recurrence (decay per head), prompt of {t}", "",
-        lambda i: ops.decayed_state_scan(q, k, v, state, o, q_start, slots, 1, num_heads=nh, decay_const=lam, silu_inputs=True), 2,
-        flops=4.0 * t * nh * dk * dv)
+    add(f"recurrence (decay per channel), prompt of {t}, pieces of {ops.SCAN_PIECE} side by side (three kernels)",
+        "Qwen2 prefill attention below (float FMA against tensor cores)",
+        lambda i: ops.decayed_state_scan(q, k, v, state, o, q_start, slots, 1, num_heads=nh, decay_pre=pre, decay_bias=bias, tau=16.0, q_scale=0.125,
+                                         pieces=pieces), 2, flops=6.0 * t * nh * dk * dv)
+    add(f"recurrence (decay per head), prompt of {t}, pieces side by side", "",
+        lambda i: ops.decayed_state_scan(q, k, v, state, o, q_start, slots, 1, num_heads=nh, decay_const=lam, silu_inputs=True, pieces=pieces), 2,
+        flops=6.0 * t * nh * dk * dv)
     # ---- rows of the residual stream
     for t in (64, 2048):
         c = 6 if t == 64 else 3

@@ -74,6 +74,91 @@ __global__ void qk_norm_cache_write_kernel(QkNormArgs a) {
     }
 }
 
+// The same for bfloat16 with every size, offset and stride a multiple of 8 elements: 16-byte accesses (a 16-byte piece
+// of a row stays whole in the cache's layout).
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float2 t = __bfloat1622float2(p[e]); f[2 * e] = t.x; f[2 * e + 1] = t.y; }
+}
+
+__global__ void qk_norm_cache_write_bf16x8_kernel(QkNormArgs a) {
+    pdl_start();
+    const int t = blockIdx.x;
+    const __nv_bfloat16* src = (const __nv_bfloat16*)a.proj + (size_t)t * a.ld;
+    const int nq8 = a.H * a.dk / 8, nk8 = a.G * a.dk / 8, nv8 = a.G * a.dv / 8;
+    const uint4* qsrc = reinterpret_cast<const uint4*>(src + a.q_off);
+    const uint4* ksrc = reinterpret_cast<const uint4*>(src + a.k_off);
+    const uint4* vsrc = reinterpret_cast<const uint4*>(src + a.v_off);
+    // both sums of squares in one pass and one reduction: the queries' in the low lanes' share, the keys' beside it
+    float sq = 0.0f, sk = 0.0f;
+    if (a.wq)
+        for (int c = threadIdx.x; c < nq8; c += blockDim.x) {
+            float f[8];
+            unpack8(qsrc[c], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sq += f[e] * f[e];
+        }
+    if (a.wk)
+        for (int c = threadIdx.x; c < nk8; c += blockDim.x) {
+            float f[8];
+            unpack8(ksrc[c], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sk += f[e] * f[e];
+        }
+    __shared__ float both[2][33];
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { both[0][warp] = sq; both[1][warp] = sk; }
+        __syncthreads();
+        if (warp == 0) {
+            const float tq = warp_sum(lane < nwarps ? both[0][lane] : 0.0f), tk = warp_sum(lane < nwarps ? both[1][lane] : 0.0f);
+            if (lane == 0) { both[0][32] = tq; both[1][32] = tk; }
+        }
+        __syncthreads();
+    }
+    const float rq = a.wq ? 1.0f / sqrtf(both[0][32] / (float)(nq8 * 8) + a.eps) : 1.0f;
+    const float rk = a.wk ? 1.0f / sqrtf(both[1][32] / (float)(nk8 * 8) + a.eps) : 1.0f;
+    auto normed = [](const uint4& raw, float r, const float* w) {
+        float f[8];
+        unpack8(raw, f);
+        uint4 out;
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&out);
+        if (w) {
+            const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+            const float g[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) p[e] = __floats2bfloat162_rn(f[2 * e] * r * g[2 * e], f[2 * e + 1] * r * g[2 * e + 1]);
+        } else {
+            out = raw;
+        }
+        return out;
+    };
+    uint4* qo = reinterpret_cast<uint4*>((__nv_bfloat16*)a.q_out + (size_t)t * nq8 * 8);
+    for (int c = threadIdx.x; c < nq8; c += blockDim.x) qo[c] = normed(qsrc[c], rq, a.wq ? a.wq + c * 8 : nullptr);
+    if (!a.write_kv) return;
+    const int pos = a.positions[t];
+    const int lp = pos / a.page, slot = pos - lp * a.page;
+    const int pg = lp < a.bt_stride ? a.block_table[(size_t)a.req_of_token[t] * a.bt_stride + lp] : -1;
+    if ((unsigned)pg >= (unsigned)a.num_pages) {
+        if (a.status && threadIdx.x == 0) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
+        return;
+    }
+    const size_t block = (size_t)a.page * a.row;
+    __nv_bfloat16* kp = (__nv_bfloat16*)a.cache + (size_t)pg * 2 * a.G * block;
+    __nv_bfloat16* vp = kp + (size_t)a.G * block;
+    for (int c = threadIdx.x; c < nk8; c += blockDim.x) {
+        const int i = c * 8, g = i / a.dk, e = i - g * a.dk;
+        *reinterpret_cast<uint4*>(kp + g * block + kv_pos(e, slot, a.row, a.page, 2)) = normed(ksrc[c], rk, a.wk ? a.wk + i : nullptr);
+    }
+    for (int c = threadIdx.x; c < nv8; c += blockDim.x) {
+        const int i = c * 8, g = i / a.dv, e = i - g * a.dv;
+        *reinterpret_cast<uint4*>(vp + g * block + kv_pos(e, slot, a.row, a.page, 2)) = vsrc[c];
+    }
+}
+
 VCB_EXPORT int vcb_qk_norm_cache_write(const void* proj, long long ld, int q_off, int k_off, int v_off, const float* wq,
                                        const float* wk, void* q_out, void* cache, const int* positions,
                                        const int* req_of_token, const int* block_table, int bt_stride, int n_tokens,
@@ -86,6 +171,12 @@ VCB_EXPORT int vcb_qk_norm_cache_write(const void* proj, long long ld, int q_off
                  H, G, dk, dv, row, page, num_pages, write_kv, eps, status};
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H * dk >= 2048 ? 512 : 256;
+    const uintptr_t addrs = (uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)wq | (uintptr_t)wk;
+    if (dtype == VCB_BF16 && !((dk | dv | row | q_off | k_off | v_off) & 7) && !(ld & 7) && !(addrs & 15)) {
+        const int chunks = H * dk / 8;
+        vcb_launch(qk_norm_cache_write_bf16x8_kernel, n_tokens, chunks >= 512 ? 256 : 128, 0, s, a);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32) vcb_launch(qk_norm_cache_write_kernel<float>, n_tokens, threads, 0, s, a);
     else if (dtype == VCB_BF16) vcb_launch(qk_norm_cache_write_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, a);
     else return VCB_ERR_BAD_ARG;

@@ -64,21 +64,26 @@ struct MmaAttnArgs {
     int bias_len;
 };
 
-// tanh through one ex2 and one division: absolute error of a few 1e-7, which is what a capped score needs
-// (tanh.approx is good to 2^-11 only, times the cap).
-__device__ __forceinline__ float tanh_ex2(float x) {
-    return 1.0f - __fdividef(2.0f, 1.0f + exp2f(x * 2.8853900817779268f));
-}
-
-// A raw product q.k into the score the softmax sees.  `dist` is clamped into the bias table; keys that the mask
-// removes afterwards may come with any distance.
-__device__ __forceinline__ float shaped_score(float raw, float scale, float cap, float inv_cap, const float* bias_row,
-                                              int dist, int bias_len) {
-    float x = raw * scale;
-    if (cap > 0.0f) x = cap * tanh_ex2(x * inv_cap);
-    if (bias_row) x += __ldg(bias_row + min(max(dist, 0), bias_len - 1));
-    return x;
-}
+// Shaped scores.  cap * tanh(x / cap) = cap - 2 cap / (1 + e^(2 x / cap)): one multiplication into the exponent's
+// units, ex2, an addition, a reciprocal and one multiply-add (ex2.approx and rcp.approx are good to 2^-22 relative:
+// the capped score is right to a few 1e-6 of the cap; tanh.approx would be good to 2^-11 only).
+struct ScoreShape {
+    float to_exp;      // scale * 2 log2(e) / cap (cap > 0), else the plain scale
+    float cap, m2cap;  // cap and -2 cap (cap > 0), else 0
+    __device__ __forceinline__ ScoreShape(float scale, float cap_) {
+        cap = cap_ > 0.0f ? cap_ : 0.0f;
+        m2cap = -2.0f * cap;
+        to_exp = cap > 0.0f ? scale * 2.8853900817779268f / cap : scale;
+    }
+    __device__ __forceinline__ float operator()(float raw) const {
+        const float x = raw * to_exp;
+        if (cap == 0.0f) return x;
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        return fmaf(m2cap, r, cap);
+    }
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -107,7 +112,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 #define LOG2E 1.4426950408889634f
-
 // Byte offset of element (row, 16-byte chunk) in a tile of rows of D bfloat16 (the Q tile, which the
 // kernels write themselves).
 template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -287,7 +291,7 @@ attention_decode_kernel(MmaAttnArgs a) {
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
     const bool shaped = a.cap > 0.0f || a.bias_t != nullptr;
     const float sl2 = (shaped ? 1.0f : a.scale) * LOG2E; // scores in units of log2 (shaped scores carry the scale already)
-    const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
+    const ScoreShape shape(a.scale, a.cap);
 
     // The splits of a request.  With split_tiles no split of any request has more than that many tiles
     // (a request's tiles are dealt evenly to the splits it needs), so a request with a long context gets
@@ -380,7 +384,9 @@ attention_decode_kernel(MmaAttnArgs a) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int j = kb + nb * 8 + (lane & 3) * 2 + (e & 1);
-                            s[nb][e] = shaped_score(s[nb][e], a.scale, a.cap, inv_cap, e < 2 ? ba : bb, pos - j, a.bias_len);
+                            float x = shape(s[nb][e]);
+                            if (a.bias_t) x += __ldg((e < 2 ? ba : bb) + min(max(pos - j, 0), a.bias_len - 1));
+                            s[nb][e] = x;
                         }
                 }
                 // only a tile that crosses lo or hi has keys to mask (the same for the whole CTA)
@@ -681,7 +687,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
     const bool shaped = a.cap > 0.0f || a.bias_t != nullptr;
     const float sl2 = (shaped ? 1.0f : a.scale) * LOG2E;
-    const float inv_cap = a.cap > 0.0f ? 1.0f / a.cap : 0.0f;
+    const ScoreShape shape(a.scale, a.cap);
 
     // [Q][K stages][V stages][barriers]
     const uint32_t sq = smem_u32(smem), sk0 = sq + Q_BYTES, sv0 = sk0 + K_STAGES * KV_BYTES;
@@ -879,7 +885,18 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             float mt = -INFINITY;
             if (shaped) {
 #pragma unroll
-                for (int i = 0; i < TKT; ++i) s[i] = shaped_score(s[i], a.scale, a.cap, inv_cap, bias_row, pos - (kb + i), a.bias_len);
+                for (int i = 0; i < TKT; ++i) s[i] = shape(s[i]);
+                if (bias_row) {
+                    const int d0 = pos - kb;                  // the distance of the tile's first key; it falls by one per key
+                    if (d0 < a.bias_len && d0 - (TKT - 1) >= 0) {
+                        const float* bp = bias_row + d0;      // the whole tile lies inside the table: no clamping
+#pragma unroll
+                        for (int i = 0; i < TKT; ++i) s[i] += __ldg(bp - i);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < TKT; ++i) s[i] += __ldg(bias_row + min(max(d0 - i, 0), a.bias_len - 1));
+                    }
+                }
             }
             if (edge) {
 #pragma unroll

@@ -20,18 +20,36 @@ template <typename T>
 __global__ void moe_router_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr,
                                   const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ wts,
                                   int width, int n_out, int top) {
-    extern __shared__ float sm[];
-    float* hrow = sm;                   // [width]
-    float* score = sm + width;          // [n_out] logits, then scores
+    extern __shared__ __align__(16) float sm[];
+    float* hrow = sm;                   // [width rounded up to 4]
+    float* score = sm + ((width + 3) & ~3);   // [n_out] logits, then scores
     float* choice = score + n_out;      // [n_out] score + correction; -inf once taken
     pdl_start();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int i = threadIdx.x; i < width; i += blockDim.x) hrow[i] = to_f32<T>(h[(size_t)t * ldh + i]);
     __syncthreads();
+    const bool vec = (width & 3) == 0 && (((uintptr_t)wr) & 15) == 0;
     for (int e = warp; e < n_out; e += nwarps) {
         const float* w = wr + (size_t)e * width;
         float acc = 0.0f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(hrow[i], w[i], acc);
+        if (vec) {
+            // 16-byte loads, two sums in flight
+            float acc2 = 0.0f;
+            int i = lane * 4;
+            for (; i + 128 < width; i += 256) {
+                const float4 a = *reinterpret_cast<const float4*>(w + i), b = *reinterpret_cast<const float4*>(w + i + 128);
+                const float4 x = *reinterpret_cast<const float4*>(hrow + i), y = *reinterpret_cast<const float4*>(hrow + i + 128);
+                acc = fmaf(x.x, a.x, fmaf(x.y, a.y, fmaf(x.z, a.z, fmaf(x.w, a.w, acc))));
+                acc2 = fmaf(y.x, b.x, fmaf(y.y, b.y, fmaf(y.z, b.z, fmaf(y.w, b.w, acc2))));
+            }
+            for (; i < width; i += 128) {
+                const float4 a = *reinterpret_cast<const float4*>(w + i), x = *reinterpret_cast<const float4*>(hrow + i);
+                acc = fmaf(x.x, a.x, fmaf(x.y, a.y, fmaf(x.z, a.z, fmaf(x.w, a.w, acc))));
+            }
+            acc += acc2;
+        } else {
+            for (int i = lane; i < width; i += 32) acc = fmaf(hrow[i], w[i], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) score[e] = acc;
     }
@@ -72,12 +90,13 @@ VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, con
                               int n_tokens, int width, int n_out, int top, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (!h || !wr || !ids || !wts || width <= 0 || n_out <= 0 || top <= 0 || top > n_out) return VCB_ERR_BAD_ARG;
-    const size_t smem = (size_t)(width + 2 * n_out) * sizeof(float);
+    const size_t smem = (size_t)(((width + 3) & ~3) + 2 * n_out) * sizeof(float);
     if (smem > 48 * 1024) return VCB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32) vcb_launch(moe_router_kernel<float>, n_tokens, 128, smem, s, (const float*)h, ldh, wr, correction, ids, wts, width, n_out, top);
+    const int threads = n_out >= 8 ? 256 : 128;          // a warp per router output at a time
+    if (dtype == VCB_F32) vcb_launch(moe_router_kernel<float>, n_tokens, threads, smem, s, (const float*)h, ldh, wr, correction, ids, wts, width, n_out, top);
     else if (dtype == VCB_BF16)
-        vcb_launch(moe_router_kernel<__nv_bfloat16>, n_tokens, 128, smem, s, (const __nv_bfloat16*)h, ldh, wr, correction, ids, wts,
+        vcb_launch(moe_router_kernel<__nv_bfloat16>, n_tokens, threads, smem, s, (const __nv_bfloat16*)h, ldh, wr, correction, ids, wts,
                    width, n_out, top);
     else return VCB_ERR_BAD_ARG;
     return vcb_last_error();

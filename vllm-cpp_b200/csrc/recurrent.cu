@@ -222,49 +222,58 @@ __global__ void decayed_state_carry_kernel(float* __restrict__ piece_state, cons
     }
 }
 
-// Grid (piece, head, tile of 64 value channels), block (64, 4): thread (x, y) owns column x for the piece's tokens
-// y, y + 4, ...; key channels pass through shared memory in slabs of 32.
+// Grid (piece, head, tile of 64 value channels), 256 threads: thread (x, y) of 16 x 16 owns columns 4x .. 4x + 3 for
+// the piece's tokens 8y .. 8y + 7 (32 sums in registers); key channels pass through shared memory in slabs of 32.
 #define INTER_MAX_TOKENS 128
 __global__ void __launch_bounds__(256)
 decayed_state_inter_kernel(const float* __restrict__ qp, long long ldqp, const float* __restrict__ piece_state, float* __restrict__ out,
                            long long ldo, const int* __restrict__ piece_start, int H, int dk, int dv) {
     __shared__ float qs[INTER_MAX_TOKENS][33];
-    __shared__ float ss[32][64];
+    __shared__ __align__(16) float ss[32][64];
     pdl_start();
-    const int p = blockIdx.x, h = blockIdx.y, col = blockIdx.z * 64 + threadIdx.x;
+    const int p = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int col0 = blockIdx.z * 64;
     const int row0 = piece_start[p], rows = min(piece_start[p + 1] - row0, INTER_MAX_TOKENS);
     const float* S = piece_state + (((size_t)p * H + h) * dk) * dv;
-    const int tid = threadIdx.y * 64 + threadIdx.x;
-    float acc[INTER_MAX_TOKENS / 4];
+    float acc[8][4];
 #pragma unroll
-    for (int i = 0; i < INTER_MAX_TOKENS / 4; ++i) acc[i] = 0.0f;
+    for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[t][c] = 0.0f;
     for (int i0 = 0; i0 < dk; i0 += 32) {
         __syncthreads();
-        for (int idx = tid; idx < rows * 32; idx += 256) {
+        for (int idx = tid; idx < INTER_MAX_TOKENS * 32; idx += 256) {
             const int t = idx >> 5, i = idx & 31;
-            qs[t][i] = i0 + i < dk ? qp[(size_t)(row0 + t) * ldqp + h * dk + i0 + i] : 0.0f;
+            qs[t][i] = (t < rows && i0 + i < dk) ? qp[(size_t)(row0 + t) * ldqp + h * dk + i0 + i] : 0.0f;
         }
         for (int idx = tid; idx < 32 * 64; idx += 256) {
-            const int i = idx >> 6, c = blockIdx.z * 64 + (idx & 63);
+            const int i = idx >> 6, c = col0 + (idx & 63);
             ss[i][idx & 63] = (i0 + i < dk && c < dv) ? S[(size_t)(i0 + i) * dv + c] : 0.0f;
         }
         __syncthreads();
+        if (ty * 8 < rows) {
+#pragma unroll 8
+            for (int i = 0; i < 32; ++i) {
+                const float4 sv = *reinterpret_cast<const float4*>(&ss[i][tx * 4]);
 #pragma unroll
-        for (int k = 0; k < INTER_MAX_TOKENS / 4; ++k) {
-            const int t = threadIdx.y + 4 * k;
-            if (t < rows) {
-                float s = acc[k];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s = fmaf(qs[t][i], ss[i][threadIdx.x], s);
-                acc[k] = s;
+                for (int t = 0; t < 8; ++t) {
+                    const float qv = qs[ty * 8 + t][i];
+                    acc[t][0] = fmaf(qv, sv.x, acc[t][0]);
+                    acc[t][1] = fmaf(qv, sv.y, acc[t][1]);
+                    acc[t][2] = fmaf(qv, sv.z, acc[t][2]);
+                    acc[t][3] = fmaf(qv, sv.w, acc[t][3]);
+                }
             }
         }
     }
-    if (col < dv) {
 #pragma unroll
-        for (int k = 0; k < INTER_MAX_TOKENS / 4; ++k) {
-            const int t = threadIdx.y + 4 * k;
-            if (t < rows) out[(size_t)(row0 + t) * ldo + h * dv + col] += acc[k];
+    for (int t = 0; t < 8; ++t) {
+        const int tok = ty * 8 + t;
+        if (tok >= rows) continue;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = col0 + tx * 4 + c;
+            if (col < dv) out[(size_t)(row0 + tok) * ldo + h * dv + col] += acc[t][c];
         }
     }
 }
@@ -281,7 +290,7 @@ VCB_EXPORT int vcb_decayed_state_join(const float* qp, long long ldqp, float* pi
     const size_t per = (size_t)H * dk * dv;
     const int blocks = (int)((per + 255) / 256 < 1024 ? (per + 255) / 256 : 1024);
     vcb_launch(decayed_state_carry_kernel, dim3(blocks, n_reqs), 256, 0, s, piece_state, dtot, state, req_pieces, state_slots, H, dk, dv);
-    vcb_launch(decayed_state_inter_kernel, dim3(n_pieces, H, (dv + 63) / 64), dim3(64, 4), 0, s, qp, ldqp, (const float*)piece_state, out, ldo,
+    vcb_launch(decayed_state_inter_kernel, dim3(n_pieces, H, (dv + 63) / 64), 256, 0, s, qp, ldqp, (const float*)piece_state, out, ldo,
                piece_start, H, dk, dv);
     return vcb_last_error();
 }
@@ -326,6 +335,72 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ o, long long l
     }
 }
 
+// The same for bfloat16 gates and results with groups, strides and widths that are multiples of 4: four channels a
+// thread at a time (16-byte loads of o and the gain, 8-byte loads and stores of the gate and the result).
+__global__ void gated_group_norm_bf16x4_kernel(const float* __restrict__ o, long long ldo, const __nv_bfloat16* __restrict__ gate, long long ldg,
+                                               const float* __restrict__ w, int wlen, __nv_bfloat16* __restrict__ out, long long ldout,
+                                               int C, int group, int act, float eps) {
+    __shared__ float scratch[33];
+    pdl_start();
+    const float* orow = o + (size_t)blockIdx.x * ldo;
+    const __nv_bfloat16* grow = gate ? gate + (size_t)blockIdx.x * ldg : nullptr;
+    __nv_bfloat16* dst = out + (size_t)blockIdx.x * ldout;
+    auto finish = [&](int i, float r, const float4& v) {          // channels i .. i + 3, whose values are v
+        const float4 g = *reinterpret_cast<const float4*>(w + i % wlen);
+        float y[4] = {v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w};
+        if (grow) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(grow + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 a0 = __bfloat1622float2(p[0]), a1 = __bfloat1622float2(p[1]);
+            const float gs[4] = {a0.x, a0.y, a1.x, a1.y};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] *= act ? silu_f(gs[e]) : sigmoid_f(gs[e]);
+        }
+        uint2 packed;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&packed);
+        q[0] = __floats2bfloat162_rn(y[0], y[1]);
+        q[1] = __floats2bfloat162_rn(y[2], y[3]);
+        *reinterpret_cast<uint2*>(dst + i) = packed;
+    };
+    if (group >= C) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x * 4; i < C; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(orow + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        const float r = 1.0f / sqrtf(ss / (float)C + eps);
+        for (int i = threadIdx.x * 4; i < C; i += blockDim.x * 4) finish(i, r, *reinterpret_cast<const float4*>(orow + i));
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    if (group <= 128) {
+        // a group is at most one vector a lane: read once.  Two groups of a warp are in flight together.
+        for (int g0 = warp * group; g0 < C; g0 += 2 * nwarps * group) {
+            const int g1 = g0 + nwarps * group;
+            const bool in0 = lane * 4 < group, in1 = in0 && g1 < C;
+            const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4 v0 = in0 ? *reinterpret_cast<const float4*>(orow + g0 + lane * 4) : zero;
+            const float4 v1 = in1 ? *reinterpret_cast<const float4*>(orow + g1 + lane * 4) : zero;
+            const float s0 = warp_sum(v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w);
+            const float s1 = warp_sum(v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w);
+            if (in0) finish(g0 + lane * 4, 1.0f / sqrtf(s0 / (float)group + eps), v0);
+            if (in1) finish(g1 + lane * 4, 1.0f / sqrtf(s1 / (float)group + eps), v1);
+        }
+        return;
+    }
+    for (int g0 = warp * group; g0 < C; g0 += nwarps * group) {
+        float ss = 0.0f;
+        for (int i = lane * 4; i < group; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(orow + g0 + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)group + eps);
+        for (int i = lane * 4; i < group; i += 128) finish(g0 + i, r, *reinterpret_cast<const float4*>(orow + g0 + i));
+    }
+}
+
 VCB_EXPORT int vcb_gated_group_norm(const float* o, long long ldo, const void* gate, long long ldg, const float* w, int wlen,
                                     void* out, long long ldout, int n_tokens, int C, int group, int act, float eps,
                                     int dtype, void* stream) {
@@ -333,6 +408,15 @@ VCB_EXPORT int vcb_gated_group_norm(const float* o, long long ldo, const void* g
     if (!o || !w || !out || C <= 0 || group <= 0 || wlen <= 0) return VCB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = C >= 2048 ? 512 : C >= 512 ? 256 : 128;
+    const uintptr_t addrs = (uintptr_t)o | (uintptr_t)w;
+    if (dtype == VCB_BF16 && !((C | group | wlen) & 3) && C % group == 0 && !((ldo | ldg | ldout) & 3) && !(addrs & 15) &&
+        !(((uintptr_t)gate | (uintptr_t)out) & 7)) {
+        const int per_group_warps = group >= C ? 0 : C / group;
+        const int th = group >= C ? (C >= 4096 ? 512 : C >= 1024 ? 256 : 128) : (per_group_warps >= 8 ? 256 : 128);
+        vcb_launch(gated_group_norm_bf16x4_kernel, n_tokens, th, 0, s, o, ldo, (const __nv_bfloat16*)gate, ldg, w, wlen, (__nv_bfloat16*)out,
+                   ldout, C, group, act, eps);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32)
         vcb_launch(gated_group_norm_kernel<float>, n_tokens, threads, 0, s, o, ldo, (const float*)gate, ldg, w, wlen, (float*)out,
                    ldout, C, group, act, eps);

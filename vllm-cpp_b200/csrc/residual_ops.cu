@@ -353,12 +353,90 @@ __global__ void norm_residual_norm_kernel(const T* __restrict__ y, const float* 
     }
 }
 
+// The same for bfloat16 rows of a multiple of 8 elements that fit the CTA's registers: NCH vectors of 8 elements a
+// thread, 16-byte accesses, the row kept between the passes.
+template <int NCH>
+__global__ void norm_residual_norm_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x,
+                                                 const float* __restrict__ next_gain, __nv_bfloat16* __restrict__ next, int hidden,
+                                                 float eps, float eps_next) {
+    __shared__ float scratch[33];
+    pdl_start();
+    const size_t row = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden >> 3;
+    float v[NCH][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            const uint4 yv = *reinterpret_cast<const uint4*>(y + row + (size_t)i * 8);
+            const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&yv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(y2[e]);
+                v[c][2 * e] = f.x;
+                v[c][2 * e + 1] = f.y;
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+    float sx = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            float* xr = x + row + (size_t)i * 8;
+            const float4 x0 = *reinterpret_cast<const float4*>(xr), x1 = *reinterpret_cast<const float4*>(xr + 4);
+            const float4 g0 = *reinterpret_cast<const float4*>(gain + i * 8), g1 = *reinterpret_cast<const float4*>(gain + i * 8 + 4);
+            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[c][e] = xs[e] + (v[c][e] * r) * gs[e];
+                sx += v[c][e] * v[c][e];
+            }
+            *reinterpret_cast<float4*>(xr) = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
+            *reinterpret_cast<float4*>(xr + 4) = make_float4(v[c][4], v[c][5], v[c][6], v[c][7]);
+        }
+    }
+    if (!next) return;
+    sx = block_sum(sx, scratch);
+    const float rn = 1.0f / sqrtf(sx / (float)hidden + eps_next);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            const float4 g0 = *reinterpret_cast<const float4*>(next_gain + i * 8), g1 = *reinterpret_cast<const float4*>(next_gain + i * 8 + 4);
+            const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            uint4 pv;
+            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(v[c][2 * e] * rn * gs[2 * e], v[c][2 * e + 1] * rn * gs[2 * e + 1]);
+            *reinterpret_cast<uint4*>(next + row + (size_t)i * 8) = pv;
+        }
+    }
+}
+
 VCB_EXPORT int vcb_norm_residual_norm(const void* y, const float* gain, float* x, const float* next_gain, void* next,
                                       int n_tokens, int hidden, float eps, float eps_next, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || !y || !gain || !x || (next && !next_gain)) return VCB_ERR_BAD_ARG;
     const int threads = hidden >= 4096 ? 512 : hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
+    const uintptr_t addrs = (uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)next_gain | (uintptr_t)next;
+    if (dtype == VCB_BF16 && hidden % 8 == 0 && hidden / 8 <= 4 * 256 && !(addrs & 15)) {
+        const int nvec = hidden / 8;
+        const int vt = nvec >= 256 ? 256 : (nvec + 31) / 32 * 32;
+        const int nch = (nvec + vt - 1) / vt;
+        const __nv_bfloat16* yb = (const __nv_bfloat16*)y;
+        __nv_bfloat16* nb = (__nv_bfloat16*)next;
+        if (nch == 1) vcb_launch(norm_residual_norm_bf16x8_kernel<1>, n_tokens, vt, 0, s, yb, gain, x, next_gain, nb, hidden, eps, eps_next);
+        else if (nch == 2) vcb_launch(norm_residual_norm_bf16x8_kernel<2>, n_tokens, vt, 0, s, yb, gain, x, next_gain, nb, hidden, eps, eps_next);
+        else vcb_launch(norm_residual_norm_bf16x8_kernel<4>, n_tokens, vt, 0, s, yb, gain, x, next_gain, nb, hidden, eps, eps_next);
+        return vcb_last_error();
+    }
     if (dtype == VCB_F32)
         vcb_launch(norm_residual_norm_kernel<float, 16>, n_tokens, threads, 0, s, (const float*)y, gain, x, next_gain, (float*)next,
                    hidden, eps, eps_next);
