@@ -390,6 +390,31 @@ def test_whole_prompts_and_the_first_tokens(tmp_path, name, dtype):
     assert cache.num_free_pages() == 16
 
 
+# models of one kind of layer: no pages at all (state slots only), and pages in every layer
+CFG_ONLY_GLA = config([gla(2, 16, 32, tau=8.0, rank=5, mlp=dense(40)), gla(4, 8, 16, tau=2.0, rank=2, mlp=None)], width=48, vocab=97)
+CFG_ONLY_PARALLEL = config([par(2, 1, 16, 16, 9, 2, 8, 16, (0.7, 0.95), mlp=moe(24, 2, 1, 2)),
+                            par(4, 2, 8, 24, 40, 1, 16, 8, (0.99,), cap=0.0, mlp=dense(64))], width=40, vocab=120, emb=6.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["gla", "parallel"])
+def test_models_of_one_kind_of_layer(tmp_path, which, dtype):
+    cfg = CFG_ONLY_GLA if which == "gla" else CFG_ONLY_PARALLEL
+    cfg, w, _, cache, runner = build(tmp_path, which, dtype, 12, cfg_page=(cfg, 16))
+    assert bool(cache.paged) == (which == "parallel")
+    rp = Replayer(runner, cache)
+    n = 140
+    ids = ids_of(cfg, w, n, 3, dtype)
+    want = plain.forward(cfg, w, ids)
+    t = 0
+    for s in (50, 1, 1, 80, 2, 1, 1, 1, 1, 1, 1):
+        rp.step([("r", ids[t: t + s], range(s))])
+        t += s
+    assert t == n
+    cache.free_request("r")
+    compare(rp.logits_of("r", range(n)), want, dtype, f"only {which}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_prefill_against_token_by_token_and_long_decoding(tmp_path, name, dtype):

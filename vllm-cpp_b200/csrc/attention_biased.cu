@@ -92,8 +92,22 @@ __global__ void qk_norm_cache_write_bf16x8_kernel(QkNormArgs a) {
     const uint4* vsrc = reinterpret_cast<const uint4*>(src + a.v_off);
     // both sums of squares in one pass and one reduction: the queries' in the low lanes' share, the keys' beside it
     float sq = 0.0f, sk = 0.0f;
+    // a thread's first four pieces of the query row stay in registers for the second pass
+    constexpr int KEEP = 4;
+    uint4 kept[KEEP];
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        kept[j] = c < nq8 ? qsrc[c] : make_uint4(0, 0, 0, 0);
+        if (a.wq) {
+            float f[8];
+            unpack8(kept[j], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sq += f[e] * f[e];
+        }
+    }
     if (a.wq)
-        for (int c = threadIdx.x; c < nq8; c += blockDim.x) {
+        for (int c = threadIdx.x + KEEP * blockDim.x; c < nq8; c += blockDim.x) {
             float f[8];
             unpack8(qsrc[c], f);
 #pragma unroll
@@ -137,7 +151,12 @@ __global__ void qk_norm_cache_write_bf16x8_kernel(QkNormArgs a) {
         return out;
     };
     uint4* qo = reinterpret_cast<uint4*>((__nv_bfloat16*)a.q_out + (size_t)t * nq8 * 8);
-    for (int c = threadIdx.x; c < nq8; c += blockDim.x) qo[c] = normed(qsrc[c], rq, a.wq ? a.wq + c * 8 : nullptr);
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nq8) qo[c] = normed(kept[j], rq, a.wq ? a.wq + c * 8 : nullptr);
+    }
+    for (int c = threadIdx.x + KEEP * blockDim.x; c < nq8; c += blockDim.x) qo[c] = normed(qsrc[c], rq, a.wq ? a.wq + c * 8 : nullptr);
     if (!a.write_kv) return;
     const int pos = a.positions[t];
     const int lp = pos / a.page, slot = pos - lp * a.page;

@@ -373,7 +373,8 @@ __global__ void gated_group_norm_bf16x4_kernel(const float* __restrict__ o, long
         for (int i = threadIdx.x * 4; i < C; i += blockDim.x * 4) finish(i, r, *reinterpret_cast<const float4*>(orow + i));
         return;
     }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    // with few tokens a row's groups are dealt to gridDim.y blocks, so that every warp has one round of work
+    const int lane = threadIdx.x & 31, nwarps = (blockDim.x >> 5) * gridDim.y, warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (group <= 128) {
         // a group is at most one vector a lane: read once.  Two groups of a warp are in flight together.
         for (int g0 = warp * group; g0 < C; g0 += 2 * nwarps * group) {
@@ -411,9 +412,14 @@ VCB_EXPORT int vcb_gated_group_norm(const float* o, long long ldo, const void* g
     const uintptr_t addrs = (uintptr_t)o | (uintptr_t)w;
     if (dtype == VCB_BF16 && !((C | group | wlen) & 3) && C % group == 0 && !((ldo | ldg | ldout) & 3) && !(addrs & 15) &&
         !(((uintptr_t)gate | (uintptr_t)out) & 7)) {
-        const int per_group_warps = group >= C ? 0 : C / group;
-        const int th = group >= C ? (C >= 4096 ? 512 : C >= 1024 ? 256 : 128) : (per_group_warps >= 8 ? 256 : 128);
-        vcb_launch(gated_group_norm_bf16x4_kernel, n_tokens, th, 0, s, o, ldo, (const __nv_bfloat16*)gate, ldg, w, wlen, (__nv_bfloat16*)out,
+        const int groups = group >= C ? 1 : C / group;
+        const int th = group >= C ? (C >= 4096 ? 512 : C >= 1024 ? 256 : 128) : (groups >= 8 ? 256 : 128);
+        int split = 1;
+        if (groups > 1 && n_tokens <= 256) {
+            split = (groups + 2 * (th / 32) - 1) / (2 * (th / 32));
+            if (split > 8) split = 8;
+        }
+        vcb_launch(gated_group_norm_bf16x4_kernel, dim3(n_tokens, split), th, 0, s, o, ldo, (const __nv_bfloat16*)gate, ldg, w, wlen, (__nv_bfloat16*)out,
                    ldout, C, group, act, eps);
         return vcb_last_error();
     }
