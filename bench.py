@@ -978,10 +978,10 @@ def retodra_kernels(z, peaks):
 
         reach = min(E, t * top)
         if t <= 128:
-            add(f"routed experts ({top} of {E}, five kernels), {t} tokens", "", run_moe, 3, bytes_=reach * 3 * ff * h * 2)
+            add(f"routed experts ({top} of {E}, six kernels), {t} tokens", "", run_moe, 3, bytes_=reach * 3 * ff * h * 2)
             add(f"Qwen2: gated feed-forward of width {top * ff}, {t} tokens", "like the one above", run_dense, 3, bytes_=3 * top * ff * h * 2)
         else:
-            add(f"routed experts ({top} of {E}, five kernels), {t} tokens", "", run_moe, 3, flops=6.0 * t * top * ff * h)
+            add(f"routed experts ({top} of {E}, six kernels), {t} tokens", "", run_moe, 3, flops=6.0 * t * top * ff * h)
             add(f"Qwen2: gated feed-forward of width {top * ff}, {t} tokens", "like the one above", run_dense, 3, flops=6.0 * t * top * ff * h)
     ops.check_status()
     return rows

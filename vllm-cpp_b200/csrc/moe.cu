@@ -1,6 +1,6 @@
 // A feed-forward of many small experts of which every token uses a few, without the host in the loop:
 //
-//   moe_router_kernel        logits = W_r h in float, softmax over all router outputs, the `top` outputs with the
+//   moe_router_*_kernel      logits = W_r h in float, softmax over all router outputs, the `top` outputs with the
 //                            largest (score + correction) chosen, their plain scores kept as weights
 //   moe_sort_kernel          the (token, choice) pairs grouped by expert: a row for each pair in a list sorted by
 //                            expert, and the list's tiles of up to TM rows of one expert
@@ -16,50 +16,77 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------- router
+// Two kernels.  Logits: a CTA takes RT_TOK tokens and eight router outputs, a warp per output: the tokens' rows pass
+// through shared memory in slabs (as float), a row of the float32 router matrix is read once for the CTA's tokens
+// with 16-byte loads.  Selection: a warp per token does the softmax over all outputs, adds the correction and
+// picks the `top` largest (the lower index wins among equals); the plain scores of the chosen are the weights.
+#define RT_TOK 4
+#define RT_SLAB 2048
+
 template <typename T>
-__global__ void moe_router_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr,
-                                  const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ wts,
-                                  int width, int n_out, int top) {
-    extern __shared__ __align__(16) float sm[];
-    float* hrow = sm;                   // [width rounded up to 4]
-    float* score = sm + ((width + 3) & ~3);   // [n_out] logits, then scores
-    float* choice = score + n_out;      // [n_out] score + correction; -inf once taken
+__global__ void __launch_bounds__(256)
+moe_router_logits_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr, float* __restrict__ logits,
+                         int n_tokens, int width, int n_out) {
+    __shared__ __align__(16) float rows[RT_TOK][RT_SLAB];
     pdl_start();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) hrow[i] = to_f32<T>(h[(size_t)t * ldh + i]);
-    __syncthreads();
+    const int t0 = blockIdx.x * RT_TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * 8 + warp;
     const bool vec = (width & 3) == 0 && (((uintptr_t)wr) & 15) == 0;
-    for (int e = warp; e < n_out; e += nwarps) {
-        const float* w = wr + (size_t)e * width;
-        float acc = 0.0f;
-        if (vec) {
-            // 16-byte loads, two sums in flight
-            float acc2 = 0.0f;
-            int i = lane * 4;
-            for (; i + 128 < width; i += 256) {
-                const float4 a = *reinterpret_cast<const float4*>(w + i), b = *reinterpret_cast<const float4*>(w + i + 128);
-                const float4 x = *reinterpret_cast<const float4*>(hrow + i), y = *reinterpret_cast<const float4*>(hrow + i + 128);
-                acc = fmaf(x.x, a.x, fmaf(x.y, a.y, fmaf(x.z, a.z, fmaf(x.w, a.w, acc))));
-                acc2 = fmaf(y.x, b.x, fmaf(y.y, b.y, fmaf(y.z, b.z, fmaf(y.w, b.w, acc2))));
-            }
-            for (; i < width; i += 128) {
-                const float4 a = *reinterpret_cast<const float4*>(w + i), x = *reinterpret_cast<const float4*>(hrow + i);
-                acc = fmaf(x.x, a.x, fmaf(x.y, a.y, fmaf(x.z, a.z, fmaf(x.w, a.w, acc))));
-            }
-            acc += acc2;
-        } else {
-            for (int i = lane; i < width; i += 32) acc = fmaf(hrow[i], w[i], acc);
+    float acc[RT_TOK];
+#pragma unroll
+    for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.0f;
+    for (int s0 = 0; s0 < width; s0 += RT_SLAB) {
+        const int len = min(RT_SLAB, width - s0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < RT_TOK * len; idx += 256) {
+            const int t = idx / len, i = idx - t * len;
+            rows[t][i] = t0 + t < n_tokens ? to_f32<T>(h[(size_t)(t0 + t) * ldh + s0 + i]) : 0.0f;
         }
-        acc = warp_sum(acc);
-        if (lane == 0) score[e] = acc;
+        __syncthreads();
+        if (e < n_out) {
+            const float* w = wr + (size_t)e * width + s0;
+            if (vec) {
+                for (int i = lane * 4; i < len; i += 128) {
+                    const float4 a = *reinterpret_cast<const float4*>(w + i);
+#pragma unroll
+                    for (int t = 0; t < RT_TOK; ++t) {
+                        const float4 x = *reinterpret_cast<const float4*>(&rows[t][i]);
+                        acc[t] = fmaf(x.x, a.x, fmaf(x.y, a.y, fmaf(x.z, a.z, fmaf(x.w, a.w, acc[t]))));
+                    }
+                }
+            } else {
+                for (int i = lane; i < len; i += 32) {
+                    const float a = w[i];
+#pragma unroll
+                    for (int t = 0; t < RT_TOK; ++t) acc[t] = fmaf(rows[t][i], a, acc[t]);
+                }
+            }
+        }
     }
-    __syncthreads();
-    if (warp != 0) return;
+    if (e >= n_out) return;
+#pragma unroll
+    for (int t = 0; t < RT_TOK; ++t) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && t0 + t < n_tokens) logits[(size_t)(t0 + t) * n_out + e] = v;
+    }
+}
+
+__global__ void __launch_bounds__(128)
+moe_router_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ ids,
+                         float* __restrict__ wts, int n_tokens, int n_out, int top) {
+    extern __shared__ float sm[];
+    pdl_start();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= n_tokens) return;
+    float* score = sm + (size_t)warp * 2 * n_out;      // [n_out] scores
+    float* choice = score + n_out;                     // [n_out] score + correction; -inf once taken
+    const float* z = logits + (size_t)t * n_out;
     float m = -INFINITY;
-    for (int e = lane; e < n_out; e += 32) m = fmaxf(m, score[e]);
+    for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
     m = warp_max(m);
     float sum = 0.0f;
-    for (int e = lane; e < n_out; e += 32) { const float p = expf(score[e] - m); score[e] = p; sum += p; }
+    for (int e = lane; e < n_out; e += 32) { const float p = expf(z[e] - m); score[e] = p; sum += p; }
     sum = warp_sum(sum);
     for (int e = lane; e < n_out; e += 32) {
         score[e] = score[e] / sum;
@@ -86,19 +113,20 @@ __global__ void moe_router_kernel(const T* __restrict__ h, long long ldh, const 
     }
 }
 
-VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, const float* correction, int* ids, float* wts,
-                              int n_tokens, int width, int n_out, int top, int dtype, void* stream) {
+// logits: float scratch [n_tokens, n_out].
+VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, const float* correction, float* logits, int* ids,
+                              float* wts, int n_tokens, int width, int n_out, int top, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (!h || !wr || !ids || !wts || width <= 0 || n_out <= 0 || top <= 0 || top > n_out) return VCB_ERR_BAD_ARG;
-    const size_t smem = (size_t)(((width + 3) & ~3) + 2 * n_out) * sizeof(float);
-    if (smem > 48 * 1024) return VCB_ERR_UNSUPPORTED;
+    if (!h || !wr || !logits || !ids || !wts || width <= 0 || n_out <= 0 || top <= 0 || top > n_out) return VCB_ERR_BAD_ARG;
+    const size_t smem = (size_t)4 * 2 * n_out * sizeof(float);
+    if (smem > 48 * 1024 || (n_out + 7) / 8 > 65535) return VCB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = n_out >= 8 ? 256 : 128;          // a warp per router output at a time
-    if (dtype == VCB_F32) vcb_launch(moe_router_kernel<float>, n_tokens, threads, smem, s, (const float*)h, ldh, wr, correction, ids, wts, width, n_out, top);
+    dim3 grid((n_tokens + RT_TOK - 1) / RT_TOK, (n_out + 7) / 8);
+    if (dtype == VCB_F32) vcb_launch(moe_router_logits_kernel<float>, grid, 256, 0, s, (const float*)h, ldh, wr, logits, n_tokens, width, n_out);
     else if (dtype == VCB_BF16)
-        vcb_launch(moe_router_kernel<__nv_bfloat16>, n_tokens, threads, smem, s, (const __nv_bfloat16*)h, ldh, wr, correction, ids, wts,
-                   width, n_out, top);
+        vcb_launch(moe_router_logits_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)h, ldh, wr, logits, n_tokens, width, n_out);
     else return VCB_ERR_BAD_ARG;
+    vcb_launch(moe_router_select_kernel, (n_tokens + 3) / 4, 128, smem, s, (const float*)logits, correction, ids, wts, n_tokens, n_out, top);
     return vcb_last_error();
 }
 

@@ -64,7 +64,7 @@ _SIGNATURES = {
     "vcb_scaled_sum": [_P, _P, _P, _L, _F, _F, _I, _P],
     "vcb_qk_norm_cache_write": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
     "vcb_attention_biased": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _I, _P],
-    "vcb_moe_router": [_P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_moe_router": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "vcb_moe_sort": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "vcb_moe_expert_gemm": [_P, _L, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _I, _P],
     "vcb_moe_combine": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -1051,18 +1051,21 @@ def moe_max_tiles(n_tokens: int, top: int, n_experts: int, tm: int) -> int:
 
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
-               weights: torch.Tensor) -> None:
+               weights: torch.Tensor, logits: torch.Tensor) -> None:
     """For every row of h: scores = softmax(w_router h) in float32 over all router outputs; ids [n, top] = the outputs
-    with the largest score + correction (the lower index wins among equals), weights [n, top] = their plain scores."""
+    with the largest score + correction (the lower index wins among equals), weights [n, top] = their plain scores.
+    ``logits``: float32 scratch [n, router outputs].  Two kernels (csrc/moe.cu)."""
     n, width = h.shape
     _rows(h, "h", h.dtype)
     top = ids.shape[1]
     _need(w_router.shape[1] == width and ids.shape == (n, top) and weights.shape == (n, top), "moe_router: shapes")
     _need(correction is None or correction.numel() == w_router.shape[0], "moe_router: one correction per router output")
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.numel() >= n * w_router.shape[0], "moe_router: logits scratch")
     _check(lib().vcb_moe_router(h.data_ptr(), h.stride(0), _dev(w_router, "w_router", torch.float32),
                                 None if correction is None else _dev(correction, "correction", torch.float32),
-                                _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), n, width,
+                                logits.data_ptr(), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), n, width,
                                 w_router.shape[0], top, dtype_code(h.dtype), _stream()), "moe_router")
+    add_launches(1)                # logits and selection
 
 
 def moe_sort(ids: torch.Tensor, n_experts: int, tm: int, sorted_token, pos, tile_expert, tile_row0, tile_rows, meta) -> None:

@@ -8,7 +8,7 @@ Outputs 0 .. num_experts - 1 are small gated feed-forwards with tensors ``e<i>.g
 g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), W_down (g * sigmoid(alpha * g) * (u + 1)).  The last
 ``num_identity`` outputs are identity experts, expert(h) = h, without tensors.
 
-Everything runs on the device (csrc/moe.cu): the router, a sort of the (token, choice) pairs by expert, one product
+Everything runs on the device (csrc/moe.cu): the router (logits, then selection), a sort of the (token, choice) pairs by expert, one product
 per tile of an expert's rows for gate-and-up (with the activation) and one for down, and the weighted sum.  The
 grids are sized for the most tiles a step can have, so a step's launches do not depend on the routing and the host
 never reads it.  The reference has no routed feed-forward (src/layers/mlp.cpp).
@@ -61,7 +61,8 @@ class RoutedExperts(FeedForward):
         pairs = n_tokens * self.top
         tiles = max(ops.moe_max_tiles(n_tokens, self.top, self.E, tm) for tm in ops.MOE_TILE_ROWS)
         ints = 3 * workspace_piece((pairs,), torch.int32) + 3 * workspace_piece((tiles,), torch.int32) + workspace_piece((4,), torch.int32)
-        return (ints + workspace_piece((pairs,), torch.float32) + workspace_piece((pairs, self.ff), self.dtype)
+        return (ints + workspace_piece((pairs,), torch.float32) + workspace_piece((n_tokens, self.E + self.I), torch.float32)
+                + workspace_piece((pairs, self.ff), self.dtype)
                 + workspace_piece((pairs, self.hidden), torch.float32))
 
     def forward(self, x, out, step, ws):
@@ -76,7 +77,8 @@ class RoutedExperts(FeedForward):
         pos = ws.take((pairs,), torch.int32)
         tile_expert, tile_row0, tile_rows = (ws.take((tiles,), torch.int32) for _ in range(3))
         meta = ws.take((4,), torch.int32)
-        ops.moe_router(x, self.w_router, self.correction, ids, weights)
+        logits = ws.take((n, self.E + self.I), torch.float32)
+        ops.moe_router(x, self.w_router, self.correction, ids, weights, logits)
         ops.moe_sort(ids, self.E, tm, sorted_token, pos, tile_expert, tile_row0, tile_rows, meta)
         act = ws.take((pairs, self.ff), self.dtype)
         lists = (sorted_token, tile_expert, tile_row0, tile_rows, meta, tiles, tm)
