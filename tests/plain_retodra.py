@@ -290,7 +290,7 @@ def tensor_shapes(cfg):
             s[p + n] = (W,)
         if layer["type"] == "gla":
             H, d, e = m["heads"], m["dim"], m["vdim"]
-            rank = m.get("decay_rank", 16)
+            rank = m.get("decay_rank", 8)
             s.update({p + "mix.q": (H * d, W), p + "mix.k": (H * d, W), p + "mix.v": (H * e, W), p + "mix.g": (H * e, W),
                       p + "mix.o": (W, H * e), p + "mix.norm": (e,), p + "mix.a1": (rank, W), p + "mix.a2": (H * d, rank),
                       p + "mix.a2.b": (H * d,)})

@@ -112,7 +112,7 @@ def test_a_mixer_with_two_caches_gets_both():
     assert cm.num_free_pages() == 12
 
 
-@pytest.mark.parametrize("rows,reach,window", [(12, 40, 20), (32, 240, 72), (7, 9.5, 0), (16, 64, 200), (2, 3, 5)])
+@pytest.mark.parametrize("rows,reach,window", [(12, 40, 20), (32, 200, 90), (7, 9.5, 0), (16, 64, 200), (2, 3, 5)])
 def test_bias_rows_by_distance(rows, reach, window):
     from vllm_cpp_b200.parts.biased_attention import distance_buckets
     count = 300
@@ -128,7 +128,7 @@ def test_random_weights_mode_fills_free_sizes(tmp_path):
     from vllm_cpp_b200.weights.safetensors_io import SafetensorsFile
     write_random_model(str(tmp_path), SAMPLE, seed=3, dtype="bfloat16")
     f = SafetensorsFile(str(tmp_path / "model.safetensors"))
-    assert tuple(f.shape("l1.mix.left.rel")) == (32, 4) and tuple(f.shape("l0.mix.a1")) == (16, 64)
-    assert tuple(f.shape("l0.mix.a2")) == (48, 16)
+    assert tuple(f.shape("l1.mix.left.rel")) == (64, 4) and tuple(f.shape("l0.mix.a1")) == (32, 64)
+    assert tuple(f.shape("l0.mix.a2")) == (48, 32)
     w = f.tensor("l0.norm1").float()
     assert abs(float(w.mean())) < 0.05                          # stored around zero

@@ -24,7 +24,7 @@ DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 # key and value sizes that differ, three query heads per kv head, a window, a cap, identity experts, a constant decay of 1
 CFG_A = config([gla(3, 16, 24, tau=4.0, rank=8, mlp=dense(96)),
                 par(6, 2, 32, 16, 20, 2, 16, 32, (0.9, 1.0), scale=0.3, cap=12.0, reach=40, rows=12, mlp=moe(40, 5, 2, 3)),
-                gla(2, 48, 8, tau=16.0, rank=4, mlp=moe(24, 3, 0, 1, limit=0.7)),
+                gla(2, 48, 8, tau=12.0, rank=4, mlp=moe(24, 3, 0, 1, limit=0.7)),
                 par(2, 2, 64, 64, 33, 3, 40, 24, (0.5, 0.97, 0.999), scale=0.125, cap=30.0, reach=100, rows=32, ls=0.7, rs=1.1,
                     mlp=dense(72))])
 # widths with odd factors, an odd vocabulary, no cap, one layer that sees every key and one that sees only itself, a layer
@@ -94,7 +94,7 @@ def build(tmp_path, name, dtype, num_pages, seed=1, max_seqs=4, graphs=False, cf
 
 # ------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,dk,dv,kind", [(3, 16, 24, "channel"), (2, 48, 64, "channel"), (1, 40, 8, "channel"), (2, 96, 80, "head"),
+@pytest.mark.parametrize("H,dk,dv,kind", [(3, 16, 24, "channel"), (2, 56, 64, "channel"), (1, 40, 8, "channel"), (2, 96, 80, "head"),
                                           (4, 64, 64, "head"), (1, 300, 33, "channel")])
 def test_recurrence_under_every_cut_with_slots_used_again(dtype, H, dk, dv, kind):
     """Requests of unequal length fed in portions of changing size, several in one launch, slots given back and taken
@@ -157,7 +157,7 @@ def test_recurrence_under_every_cut_with_slots_used_again(dtype, H, dk, dv, kind
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,dk,dv,kind", [(2, 48, 64, "channel"), (3, 16, 24, "head"), (1, 72, 130, "channel")])
+@pytest.mark.parametrize("H,dk,dv,kind", [(2, 56, 64, "channel"), (3, 16, 24, "head"), (1, 72, 130, "channel")])
 def test_recurrence_in_pieces_side_by_side(dtype, H, dk, dv, kind):
     """Long portions cut into pieces that run side by side and are joined: the same outputs and the same final state
     as token by token, for a long request beside a short one, over two steps."""
@@ -263,7 +263,7 @@ def attention_harness(att, page, pages, max_len, max_seqs=3):
 
 @pytest.mark.parametrize("dtype,H,G,dk,dv,window,page,cap,plain_kernel", [
     ("float32", 4, 2, 32, 16, 20, 16, 12.0, True), ("float32", 3, 3, 24, 40, 37, 16, 0.0, True), ("float32", 2, 1, 8, 8, 0, 16, 3.0, True),
-    ("bfloat16", 8, 2, 64, 64, 72, 16, 20.0, False), ("bfloat16", 8, 2, 64, 64, 72, 16, 20.0, True), ("bfloat16", 2, 1, 128, 128, 33, 32, 8.0, False),
+    ("bfloat16", 6, 2, 64, 64, 70, 16, 18.0, False), ("bfloat16", 6, 2, 64, 64, 70, 16, 18.0, True), ("bfloat16", 2, 1, 128, 128, 33, 32, 8.0, False),
     ("bfloat16", 4, 4, 64, 64, 1, 16, 5.0, False), ("bfloat16", 20, 1, 64, 64, 0, 16, 0.0, False), ("bfloat16", 6, 2, 128, 128, 130, 16, 30.0, False),
     ("bfloat16", 3, 1, 48, 80, 50, 16, 10.0, True)])
 def test_attention_with_planted_keys(dtype, H, G, dk, dv, window, page, cap, plain_kernel):
@@ -529,7 +529,7 @@ def random_retodra_config(rng):
             mlp = moe(int(rng.integers(8, 60)), experts, identity, int(rng.integers(1, experts + identity + 1)), limit=float(rng.uniform(0.5, 3)))
         if rng.random() < 0.5:
             layers.append(gla(int(rng.integers(1, 7)), int(rng.choice([4, 8, 12, 16, 40, 72])), int(rng.choice([8, 16, 33, 64])),
-                              tau=float(rng.choice([1.0, 4.0, 16.0])), rank=int(rng.integers(1, 20)), mlp=mlp))
+                              tau=float(rng.choice([1.0, 4.0, 12.0])), rank=int(rng.integers(1, 20)), mlp=mlp))
         else:
             g = int(rng.integers(1, 4))
             rh = int(rng.integers(1, 5))

@@ -92,9 +92,10 @@ class RetodraConfig:
                     problems.append(f"{mw}'left' and {mw}'right' must be objects")
                     continue
                 lw, rw = mw + "left.", mw + "right."
-                lm = numbers(left, lw, integers=("heads", "kv_heads", "dim", "vdim"), reals=("scale", "bias_max"))
-                cap = left.get("softcap")
-                lm["softcap"] = 0.0 if cap is None else float(number(left, "softcap", lw))
+                lm = numbers(left, lw, integers=("heads", "dim", "vdim"), reals=("scale", "bias_max"))
+                lm["kv_heads"] = lm["heads"] if left.get("kv_heads") is None else number(left, "kv_heads", lw, integer=True)
+                cap = left.get("softcap")           # absent or 0: scores are not capped
+                lm["softcap"] = 0.0 if not cap and not isinstance(cap, bool) else float(number(left, "softcap", lw))
                 mask = left.get("mask")
                 lm["window"] = 0 if mask is None else number(mask, "size", lw + "mask.", integer=True)
                 if lm["heads"] % lm["kv_heads"]:

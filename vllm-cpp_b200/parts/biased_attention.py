@@ -32,7 +32,7 @@ from ..csrc import ops
 from .attention import PagedAttentionKernels
 from .base import PagedKVSpec, ParamSpec, register_mixer, workspace_piece
 
-DEFAULT_BIAS_ROWS = 32       # rows of the bias table where no checkpoint gives them (random weights)
+DEFAULT_BIAS_ROWS = 64       # rows of the bias table where no checkpoint gives them (random weights)
 
 
 def distance_buckets(rows: int, reach: float, count: int) -> np.ndarray:

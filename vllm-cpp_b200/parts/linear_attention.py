@@ -27,7 +27,7 @@ import torch
 from ..csrc import ops
 from .base import Mixer, ParamSpec, StateSpec, register_mixer, workspace_piece
 
-DEFAULT_DECAY_RANK = 16      # inner width of the decay's two products where no checkpoint gives it (random weights)
+DEFAULT_DECAY_RANK = 32      # inner width of the decay's two products where no checkpoint gives it (random weights)
 
 
 class DecayedStateMixer(Mixer):
