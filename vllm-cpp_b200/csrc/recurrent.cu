@@ -51,7 +51,7 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return z < 0.0f ? z - 
 // y * DKP .. y * DKP + DKP - 1 of column x of S in registers.  Key channels beyond dk are padded with k = q = 0.
 template <typename T, int DKP>
 __global__ void decayed_state_scan_kernel(ScanArgs a) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     pdl_start();
     const int r = blockIdx.x, h = blockIdx.y, dvt = blockDim.x, col0 = blockIdx.z * dvt;
     const int tx = threadIdx.x, part = threadIdx.y, parts = blockDim.y;
@@ -83,26 +83,40 @@ __global__ void decayed_state_scan_kernel(ScanArgs a) {
     for (int c0 = row0; c0 < row1; c0 += TC) {
         const int tc = min(TC, row1 - c0);
         __syncthreads();                          // the chunk before has been read
-        for (int idx = tid; idx < tc * dkpad; idx += nthreads) {
-            const int tt = idx / dkpad, i = idx - tt * dkpad;
-            float qv = 0.0f, kv = 0.0f, av = 1.0f;
-            if (i < a.dk) {
-                const size_t row = (size_t)(c0 + tt);
-                const int c = h * a.dk + i;
-                qv = to_f32<T>(q[row * a.ldq + c]);
-                kv = to_f32<T>(k[row * a.ldk + c]);
-                if (a.act) { qv = silu_f(qv); kv = silu_f(kv); }
-                qv *= a.q_scale;
-                if (dp) {
-                    const float z = to_f32<T>(dp[row * a.ldd + c]) + (a.decay_bias ? a.decay_bias[c] : 0.0f);
-                    av = expf(log_sigmoid_f(z) * a.inv_tau);
-                } else {
-                    av = dconst;
+        // four elements a thread at a time: all their loads are issued before the first is used
+        for (int base = tid; base < tc * dkpad; base += 4 * nthreads) {
+            float rq[4], rk[4], rz[4];
+            bool in[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int idx = base + j * nthreads;
+                const int tt = idx / dkpad, i = idx - tt * dkpad;
+                in[j] = idx < tc * dkpad && i < a.dk;
+                rq[j] = rk[j] = rz[j] = 0.0f;
+                if (in[j]) {
+                    const size_t row = (size_t)(c0 + tt);
+                    const int c = h * a.dk + i;
+                    rq[j] = to_f32<T>(q[row * a.ldq + c]);
+                    rk[j] = to_f32<T>(k[row * a.ldk + c]);
+                    if (dp) rz[j] = to_f32<T>(dp[row * a.ldd + c]) + (a.decay_bias ? a.decay_bias[c] : 0.0f);
                 }
             }
-            qs[idx] = qv;
-            ks[idx] = kv;
-            as[idx] = av;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int idx = base + j * nthreads;
+                if (idx >= tc * dkpad) continue;
+                float qv = 0.0f, kv = 0.0f, av = 1.0f;
+                if (in[j]) {
+                    qv = rq[j];
+                    kv = rk[j];
+                    if (a.act) { qv = silu_f(qv); kv = silu_f(kv); }
+                    qv *= a.q_scale;
+                    av = dp ? expf(log_sigmoid_f(rz[j]) * a.inv_tau) : dconst;
+                }
+                qs[idx] = qv;
+                ks[idx] = kv;
+                as[idx] = av;
+            }
         }
         for (int idx = tid; idx < tc * dvt; idx += nthreads) {
             const int tt = idx / dvt, j = idx - tt * dvt, c = col0 + j;
@@ -123,16 +137,24 @@ __global__ void decayed_state_scan_kernel(ScanArgs a) {
         }
         for (int tt = 0; tt < tc; ++tt) {
             const float vv = vs[tt * dvt + tx];
-            const float* qq = qs + tt * dkpad + part * DKP;
-            const float* kk = ks + tt * dkpad + part * DKP;
-            const float* aa = as + tt * dkpad + part * DKP;
-            float acc = 0.0f;
+            // 16-byte reads of the token's q, k and decays (the same addresses for the whole warp); four sums in flight
+            const float4* qq = reinterpret_cast<const float4*>(qs + tt * dkpad + part * DKP);
+            const float4* kk = reinterpret_cast<const float4*>(ks + tt * dkpad + part * DKP);
+            const float4* aa = reinterpret_cast<const float4*>(as + tt * dkpad + part * DKP);
+            float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < DKP; ++i) {
-                S[i] = fmaf(aa[i], S[i], kk[i] * vv);
-                acc = fmaf(S[i], qq[i], acc);
+            for (int i = 0; i < DKP / 4; ++i) {
+                const float4 a4 = aa[i], k4 = kk[i], q4 = qq[i];
+                S[4 * i] = fmaf(a4.x, S[4 * i], k4.x * vv);
+                S[4 * i + 1] = fmaf(a4.y, S[4 * i + 1], k4.y * vv);
+                S[4 * i + 2] = fmaf(a4.z, S[4 * i + 2], k4.z * vv);
+                S[4 * i + 3] = fmaf(a4.w, S[4 * i + 3], k4.w * vv);
+                acc0 = fmaf(S[4 * i], q4.x, acc0);
+                acc1 = fmaf(S[4 * i + 1], q4.y, acc1);
+                acc2 = fmaf(S[4 * i + 2], q4.z, acc2);
+                acc3 = fmaf(S[4 * i + 3], q4.w, acc3);
             }
-            ps[(part * TC + tt) * dvt + tx] = acc;
+            ps[(part * TC + tt) * dvt + tx] = (acc0 + acc1) + (acc2 + acc3);
         }
         __syncthreads();
         for (int idx = tid; idx < tc * dvt; idx += nthreads) {
