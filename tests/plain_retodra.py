@@ -322,7 +322,7 @@ def random_weights(cfg, seed, std=None, sharp=1.0, decisive_routing=False):
     """Random weights for a configuration made by the tests ('rel_rows' in a left mixer and 'decay_rank' in a gla
     mixer are the tests' own keys: the engine reads those sizes from the tensors).  ``sharp`` scales the
     left mixers' q and k gains, so that their softmax is peaked.  ``decisive_routing``: the routers' corrections lie
-    0.4 apart in a random order, so that no rounding of the scores turns a choice (the weights still follow the scores).
+    1.5 apart in a random order (scores differ by less than 1), so that no rounding turns a choice (the weights still follow the scores).
     In a gla mixer the key matrix is the query matrix plus noise: a head's result is normed by itself, and at a
     sequence's first token it is v_0 (k_0 . q_0), whose sign would hang on the rounding of one dot product of
     unrelated vectors; with related ones the product is clearly positive and the comparison means something."""
@@ -343,7 +343,7 @@ def random_weights(cfg, seed, std=None, sharp=1.0, decisive_routing=False):
         elif leaf == "rel":
             w[name] = rng.standard_normal(shape)
         elif leaf == "correction":
-            w[name] = 0.4 * rng.permutation(shape[0]) if decisive_routing else 0.05 * rng.standard_normal(shape)
+            w[name] = 1.5 * rng.permutation(shape[0]) if decisive_routing else 0.05 * rng.standard_normal(shape)
         elif name.endswith("a2.b"):
             w[name] = 2.0 + rng.standard_normal(shape)
         elif name.endswith(".a2"):

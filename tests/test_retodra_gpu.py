@@ -485,6 +485,43 @@ def test_unequal_requests_together_on_few_pages(tmp_path, name, dtype):
     assert cache.num_free_pages() == 28 and len(set(slots_seen)) == 3
 
 
+# larger layers: heads of 128 and 64 on the tensor-core attention kernels, recurrences with 128 and 80 key channels,
+# experts whose tiles are 64 and 16 rows high, portions that run in pieces
+CFG_WIDE = config([gla(4, 128, 64, tau=8.0, rank=24, mlp=dense(640)),
+                   par(8, 2, 128, 128, 200, 4, 64, 96, (0.9, 0.97, 0.99, 1.0), scale=0.09, cap=25.0, reach=300, rows=40, mlp=moe(192, 6, 1, 2)),
+                   gla(2, 80, 128, tau=3.0, rank=7, mlp=moe(128, 3, 0, 1)),
+                   par(4, 4, 64, 64, 50, 2, 32, 64, (0.95, 0.8), scale=0.125, cap=0.0, reach=64, rows=20, mlp=dense(512))],
+                  width=384, vocab=700, emb=4.0)
+
+
+def test_bfloat16_beside_float32_at_larger_sizes(tmp_path):
+    """The same (bfloat16-valued) weights through the float32 engine, which the small configurations anchor to the plain
+    implementation, and through the bfloat16 engine with its tensor-core kernels: a prompt of 450 tokens in two portions,
+    then single tokens, beside a second request."""
+    from vllm_cpp_b200 import EngineConfig
+    from vllm_cpp_b200.engine import factory
+    w = plain.round_to_bf16(plain.random_weights(CFG_WIDE, 3, sharp=1.0, decisive_routing=True))
+    rng = np.random.default_rng(5)
+    ids = {"a": rng.integers(0, 700, size=480).tolist(), "b": rng.integers(0, 700, size=70).tolist()}
+    steps = [[("a", 300)], [("a", 150), ("b", 40)]] + [[("a", 1), ("b", 1)]] * 30
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        folder = str(tmp_path / dtype)
+        plain.write_model_folder(folder, CFG_WIDE, w, store="BF16" if dtype == "bfloat16" else "F32")
+        ecfg = EngineConfig(model_path=folder, dtype=dtype, block_size=16, num_gpu_blocks=48, max_num_seqs=2, max_model_len=768,
+                            max_num_batched_tokens=512, use_cuda_graphs=False)
+        _, cache, runner = factory.build(ecfg)
+        rp, at = Replayer(runner, cache), {"a": 0, "b": 0}
+        for step in steps:
+            rp.step([(r, ids[r][at[r]: at[r] + n], range(n)) for r, n in step])
+            for r, n in step:
+                at[r] += n
+        got[dtype] = {r: rp.logits_of(r, range(at[r])) for r in ids}
+        del runner, cache
+    for r in ids:
+        compare(got["bfloat16"][r], got["float32"][r], "bfloat16", f"larger sizes {r}")
+
+
 @pytest.mark.parametrize("dtype,name,pages", [("float32", "A", 24), ("bfloat16", "A", 24), ("float32", "B", 7)])
 def test_greedy_generation_through_the_entry_point(tmp_path, dtype, name, pages):
     """LLM.generate: the scheduler cuts the prompts under a small token budget, decode steps are captured and
@@ -582,10 +619,15 @@ def test_the_replay_program_on_configurations_drawn_at_random(tmp_path, seed, dt
     assert p.returncode == 0, p.stderr[-3000:]
     assert [l for l in p.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(len(lines))]
     want = {r: plain.forward(cfg, weights, ids[r]) for r in ids}
+    got_rows, want_rows = [], []
     for i, rows in enumerate(asked):
         if rows:
             got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
-            compare(got, np.stack([want[r][t] for r, t in rows]), dtype, f"seed {seed} step {i}: {cfg['layers']}")
+            assert got.shape[0] == len(rows), f"step {i}: {got.shape[0]} rows written, {len(rows)} asked for"
+            got_rows.append(got)
+            want_rows.append(np.stack([want[r][t] for r, t in rows]))
+    # all steps' rows together: a step has one to three rows a request, too few for a mean to mean anything
+    compare(np.concatenate(got_rows), np.concatenate(want_rows), dtype, f"seed {seed}: {cfg['layers']}")
 
 
 def test_command_line_and_sampling_options(tmp_path):
