@@ -46,12 +46,20 @@ moe_router_logits_kernel(const T* __restrict__ h, long long ldh, const float* __
         if (e < n_out) {
             const float* w = wr + (size_t)e * width + s0;
             if (vec) {
-                for (int i = lane * 4; i < len; i += 128) {
-                    const float4 a = *reinterpret_cast<const float4*>(w + i);
+                // four 16-byte pieces of the router's row in flight per lane before any is used
+                for (int i = lane * 4; i < len; i += 512) {
+                    float4 a[4];
 #pragma unroll
-                    for (int t = 0; t < RT_TOK; ++t) {
-                        const float4 x = *reinterpret_cast<const float4*>(&rows[t][i]);
-                        acc[t] = fmaf(x.x, a.x, fmaf(x.y, a.y, fmaf(x.z, a.z, fmaf(x.w, a.w, acc[t]))));
+                    for (int u = 0; u < 4; ++u)
+                        a[u] = i + u * 128 < len ? *reinterpret_cast<const float4*>(w + i + u * 128) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (i + u * 128 >= len) break;
+#pragma unroll
+                        for (int t = 0; t < RT_TOK; ++t) {
+                            const float4 x = *reinterpret_cast<const float4*>(&rows[t][i + u * 128]);
+                            acc[t] = fmaf(x.x, a[u].x, fmaf(x.y, a[u].y, fmaf(x.z, a[u].z, fmaf(x.w, a[u].w, acc[t]))));
+                        }
                     }
                 }
             } else {
